@@ -3,8 +3,9 @@
 *Groups.*  Cache layers whose mixers keep the same thing (key/value heads, head size,
 window) form a group.  A group owns its pages: a pool of page ids with a LIFO free
 list, one storage tensor ``[layers, 2, pages, kv_heads, page_size, head_dim]`` (the keys of a
-page lie together per head, so attention reads long runs) and one
-block table per request.  A page id means the same row range in every layer of its group
+page lie together per head, so attention reads long runs; a group whose values have another
+size than its keys keeps two tensors, ``[layers, pages, kv_heads, page_size, head_dim]`` and
+``[..., value_dim]``) and one block table per request.  A page id means the same row range in every layer of its group
 (the reference's pool works that way for its single group, ``cache/block_pool.py:332-351``;
 its free list is LIFO as well, ``:570,735-757``).  Groups with a window give pages back as
 soon as every position in them has fallen out of every future query's window; the table
@@ -87,6 +88,7 @@ class GroupSpec:
     kv_heads: int
     head_dim: int
     window: int | None
+    value_dim: int | None = None   # size of a value per head where it differs from head_dim
 
 
 @dataclass
@@ -116,12 +118,13 @@ def group_needs(needs: Sequence) -> list[GroupSpec]:
     for n in needs:
         if n.kv is None:
             continue
-        key = (n.kv.kv_heads, n.kv.head_dim, n.kv.window)
+        vdim = getattr(n.kv, "value_dim", None)
+        key = (n.kv.kv_heads, n.kv.head_dim, n.kv.window, None if vdim in (None, n.kv.head_dim) else vdim)
         if key not in members:
             members[key] = []
             order.append(key)
         members[key].append(n.index)
-    return [GroupSpec(tuple(members[k]), k[0], k[1], k[2]) for k in order]
+    return [GroupSpec(tuple(members[k]), k[0], k[1], k[2], k[3]) for k in order]
 
 
 class CacheManager:
@@ -175,15 +178,24 @@ class CacheManager:
         # pages handed out since the last take_table_updates(): flat (slot, index, page) triples
         self._table_updates: list[list[int]] = [[] for _ in self.groups]
 
-        self.storage: list[torch.Tensor] = []
+        self.storage: list[torch.Tensor] = []          # every tensor that holds keys or values
+        self._group_kv: list[tuple[torch.Tensor, torch.Tensor]] = []   # per group: keys, values ``[layers, pages, ...]``
         self.block_tables: list[torch.Tensor] = []
         self.state_arenas: dict[int, torch.Tensor] = {}
         if self.device is not None:
             for g, n, width in zip(self.groups, pages, self.table_width):
-                self.storage.append(
-                    torch.zeros((len(g.layers), 2, n, g.kv_heads, page_size, g.head_dim),
-                                dtype=dtype, device=self.device)
-                )
+                if g.value_dim is None:
+                    st = torch.zeros((len(g.layers), 2, n, g.kv_heads, page_size, g.head_dim),
+                                     dtype=dtype, device=self.device)
+                    self.storage.append(st)
+                    self._group_kv.append((st[:, 0], st[:, 1]))
+                else:
+                    keys = torch.zeros((len(g.layers), n, g.kv_heads, page_size, g.head_dim),
+                                       dtype=dtype, device=self.device)
+                    values = torch.zeros((len(g.layers), n, g.kv_heads, page_size, g.value_dim),
+                                         dtype=dtype, device=self.device)
+                    self.storage.extend([keys, values])
+                    self._group_kv.append((keys, values))
                 self.block_tables.append(torch.full((max_requests, width), -1, dtype=torch.int32, device=self.device))
             for need in self.needs:
                 if need.state is not None:
@@ -348,10 +360,10 @@ class CacheManager:
 
     def layer_kv(self, cache_layer: int) -> tuple[int, torch.Tensor, torch.Tensor]:
         """``(group index, keys, values)`` of a cache layer, each
-        ``[pages, kv_heads, page_size, head_dim]``."""
+        ``[pages, kv_heads, page_size, head_dim]`` (values ``[..., value_dim]`` where the group has one)."""
         gi, li = self.layer_place[cache_layer]
-        st = self.storage[gi]
-        return gi, st[li, 0], st[li, 1]
+        keys, values = self._group_kv[gi]
+        return gi, keys[li], values[li]
 
     def layer_state(self, cache_layer: int) -> torch.Tensor | None:
         return self.state_arenas.get(cache_layer)

@@ -73,6 +73,8 @@ def lookup_architecture(name: str) -> Architecture:
 
 def architecture_of(raw: Mapping[str, Any]) -> Architecture:
     archs = raw.get("architectures")
+    if not archs and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]       # some configurations name their single architecture directly
     if not archs:
         raise ConfigError("config.json has no 'architectures' entry")
     if not isinstance(archs, (list, tuple)) or not isinstance(archs[0], str):
@@ -110,4 +112,4 @@ def _load_builtin() -> None:
     if _builtin_loaded:
         return
     _builtin_loaded = True
-    from ..models import llama  # noqa: F401  (registers itself on import)
+    from ..models import llama, ruvurax  # noqa: F401  (register themselves on import)

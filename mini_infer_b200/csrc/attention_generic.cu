@@ -6,14 +6,17 @@
 // 32, so a row's arithmetic never depends on what else is in the batch), and keeps an
 // online softmax in fp32.  Keys and values are fetched through the block table; a
 // query at absolute position p sees keys j with  max(0, p - window + 1) <= j <= p
-// (window = 0: all keys up to p).
+// (window = 0: all keys up to p).  Keys and values may have different sizes per head (d for
+// queries and keys, dv for values and the output); any size from 1 to 256 is taken, sizes that are
+// no multiple of 4 element by element.
 //
 // Layouts
 //   q    [tokens, q_stride]   head h at columns [h*d, (h+1)*d)
-//   out  [tokens, out_stride] same head layout
-//   kcache, vcache [pages, nkv, page_size, d]: the page_size keys of a page lie together
-//                  per key/value head; the 16-byte chunks of a row are permuted by the key's
-//                  in-page offset (mi_swizzled in common.cuh)
+//   out  [tokens, out_stride] head h at columns [h*dv, (h+1)*dv)
+//   kcache [pages, nkv, page_size, d], vcache [pages, nkv, page_size, dv]: the page_size keys of
+//                  a page lie together per key/value head; the 16-byte chunks of a row are permuted
+//                  by the key's in-page offset (mi_swizzled in common.cuh; rows that are no whole
+//                  number of chunks are not permuted, mi_swizzle_mask_rows)
 //   block_table [rows, bt_stride] page ids; request b uses row table_rows[b] (row b when
 //                  table_rows is null);  q_start / q_len / kv_len [requests]
 //   tile_req / tile_tok0 [tiles]: request and first token (within the portion) of a tile
@@ -33,18 +36,20 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ table_rows, int page_size,
                          const int* __restrict__ q_start, const int* __restrict__ q_len,
                          const int* __restrict__ kv_len, const int* __restrict__ tile_req,
-                         const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale,
+                         const int* __restrict__ tile_tok0, int nq, int nkv, int d, int dv, float scale,
                          int window) {
   mi_pdl_enter();   // inputs come from the kernels before this one
   extern __shared__ __align__(16) float smem[];
-  float* Vs = smem;                       // [BK][d]
-  float* Qs = Vs + BK * d;                // [BQ][d]
+  float* Vs = smem;                       // [BK][dvp], dvp = dv rounded up to 4
+  const int dvp = (dv + 3) & ~3;
+  float* Qs = Vs + BK * dvp;              // [BQ][d]
   float* Ks = Qs + BQ * d;                // [BK][d + 1]
   float* Ss = Ks + BK * (d + 1);          // [BQ][BK]
   int* rowbase = reinterpret_cast<int*>(Ss + BQ * BK);  // [BK] element offset / d of each key row, -1: none
   int* rowswz = rowbase + BK;                            // [BK] chunk permutation of each key row
   constexpr int EPC = 16 / (int)sizeof(T);
-  const int swz_mask = mi_swizzle_mask(d, (int)sizeof(T));
+  const int swz_mask = mi_swizzle_mask_rows(d, (int)sizeof(T));
+  const int swz_mask_v = mi_swizzle_mask_rows(dv, (int)sizeof(T));
 
   const int tid = threadIdx.x;
   const int tile = blockIdx.x / nq, h = blockIdx.x - tile * nq;   // all heads of a tile, then the next tile (the caller lists long tiles first)
@@ -70,7 +75,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   float acc[DMAX / 8];
 #pragma unroll
   for (int e = 0; e < DMAX / 8; ++e) acc[e] = 0.f;
-  const int ne = d >> 3;  // d is a multiple of 16
+  const int ne = (dv + 7) >> 3;
 
   for (int j0 = (j_lo / BK) * BK; j0 < j_end; j0 += BK) {
     __syncthreads();  // previous chunk fully consumed (and Qs written, first time)
@@ -82,25 +87,51 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         base = (page * nkv + kvh) * page_size + j % page_size;
       }
       rowbase[tid] = base;
-      rowswz[tid] = (j % page_size) & swz_mask;
+      rowswz[tid] = (j % page_size);
     }
     __syncthreads();
-    const int d4 = d >> 2;
-    for (int idx = tid; idx < BK * d4; idx += NTHREADS) {
-      const int jj = idx / d4, k4 = (idx - jj * d4) << 2;
-      const int base = rowbase[jj];
-      float kf[4] = {0.f, 0.f, 0.f, 0.f}, vf[4] = {0.f, 0.f, 0.f, 0.f};
-      if (base >= 0) {
-        const size_t off = (size_t)base * d + ((((k4 / EPC) ^ rowswz[jj]) * EPC) + (k4 % EPC));
-        Vec4<T> kv, vv;
-        kv.load(kcache + off);
-        vv.load(vcache + off);
-        kv.get(kf);
-        vv.get(vf);
+    if ((d & 3) == 0) {
+      const int d4 = d >> 2;
+      for (int idx = tid; idx < BK * d4; idx += NTHREADS) {
+        const int jj = idx / d4, k4 = (idx - jj * d4) << 2;
+        const int base = rowbase[jj];
+        float kf[4] = {0.f, 0.f, 0.f, 0.f};
+        if (base >= 0) {
+          const size_t off = (size_t)base * d + ((((k4 / EPC) ^ (rowswz[jj] & swz_mask)) * EPC) + (k4 % EPC));
+          Vec4<T> kv;
+          kv.load(kcache + off);
+          kv.get(kf);
+        }
+        float* kd = Ks + jj * dp + k4;
+        kd[0] = kf[0]; kd[1] = kf[1]; kd[2] = kf[2]; kd[3] = kf[3];
       }
-      float* kd = Ks + jj * dp + k4;
-      kd[0] = kf[0]; kd[1] = kf[1]; kd[2] = kf[2]; kd[3] = kf[3];
-      *reinterpret_cast<float4*>(Vs + jj * d + k4) = make_float4(vf[0], vf[1], vf[2], vf[3]);
+    } else {
+      for (int idx = tid; idx < BK * d; idx += NTHREADS) {
+        const int jj = idx / d, k = idx - jj * d;
+        const int base = rowbase[jj];
+        Ks[jj * dp + k] = base >= 0 ? mi_to_float(kcache[(size_t)base * d + mi_swizzled(k, rowswz[jj], swz_mask, EPC)]) : 0.f;
+      }
+    }
+    if ((dv & 3) == 0) {
+      const int d4 = dv >> 2;
+      for (int idx = tid; idx < BK * d4; idx += NTHREADS) {
+        const int jj = idx / d4, k4 = (idx - jj * d4) << 2;
+        const int base = rowbase[jj];
+        float vf[4] = {0.f, 0.f, 0.f, 0.f};
+        if (base >= 0) {
+          const size_t off = (size_t)base * dv + ((((k4 / EPC) ^ (rowswz[jj] & swz_mask_v)) * EPC) + (k4 % EPC));
+          Vec4<T> vv;
+          vv.load(vcache + off);
+          vv.get(vf);
+        }
+        *reinterpret_cast<float4*>(Vs + jj * dvp + k4) = make_float4(vf[0], vf[1], vf[2], vf[3]);
+      }
+    } else {
+      for (int idx = tid; idx < BK * dv; idx += NTHREADS) {
+        const int jj = idx / dv, k = idx - jj * dv;
+        const int base = rowbase[jj];
+        Vs[jj * dvp + k] = base >= 0 ? mi_to_float(vcache[(size_t)base * dv + mi_swizzled(k, rowswz[jj], swz_mask_v, EPC)]) : 0.f;
+      }
     }
     __syncthreads();
 
@@ -145,18 +176,18 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     __syncthreads();
     for (int j = 0; j < BK; ++j) {
       const float pj = Ss[r * BK + j];
-      const float* vrow = Vs + j * d + c;
+      const float* vrow = Vs + j * dvp + c;
 #pragma unroll
       for (int e = 0; e < DMAX / 8; ++e)
-        if (e < ne) acc[e] = fmaf(pj, vrow[8 * e], acc[e]);
+        if (e < ne && c + 8 * e < dv) acc[e] = fmaf(pj, vrow[8 * e], acc[e]);
     }
   }
   if (r < rows && l_i > 0.f) {
     const float inv = 1.f / l_i;
-    T* orow = out + (size_t)(qs + tok0 + r) * out_stride + h * d + c;
+    T* orow = out + (size_t)(qs + tok0 + r) * out_stride + h * dv + c;
 #pragma unroll
     for (int e = 0; e < DMAX / 8; ++e)
-      if (e < ne) orow[8 * e] = mi_from_float<T>(acc[e] * inv);
+      if (e < ne && c + 8 * e < dv) orow[8 * e] = mi_from_float<T>(acc[e] * inv);
   }
 }
 
@@ -164,9 +195,9 @@ template <typename T, int DMAX>
 static int launch(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
                   const void* vcache, const int* block_table, int bt_stride, const int* table_rows, int page_size,
                   const int* q_start, const int* q_len, const int* kv_len, const int* tile_req,
-                  const int* tile_tok0, int n_tiles, int nq, int nkv, int d, float scale, int window,
+                  const int* tile_tok0, int n_tiles, int nq, int nkv, int d, int dv, float scale, int window,
                   cudaStream_t stream) {
-  const size_t smem = ((size_t)BK * d + (size_t)BQ * d + (size_t)BK * (d + 1) + BQ * BK) * sizeof(float) +
+  const size_t smem = ((size_t)BK * ((dv + 3) & ~3) + (size_t)BQ * d + (size_t)BK * (d + 1) + BQ * BK) * sizeof(float) +
                       2 * BK * sizeof(int);
   auto kern = attention_generic_kernel<T, DMAX>;
   if (smem > 48 * 1024) {
@@ -176,12 +207,48 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
   dim3 grid((unsigned)(n_tiles * nq));
   MI_LAUNCH((kern), grid, NTHREADS, smem, stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)kcache,
                                          (const T*)vcache, block_table, bt_stride, table_rows, page_size, q_start,
-                                         q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, scale, window);
+                                         q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, dv, scale, window);
   return 0;
 }
 
 extern "C" int mi_attention_generic_tile_tokens() { return BQ; }
 
+extern "C" int mi_attention_generic_kv(const void* q, int q_stride, void* out, int out_stride,
+                                       const void* kcache, const void* vcache, const int* block_table,
+                                       int bt_stride, const int* table_rows, int page_size, const int* q_start,
+                                       const int* q_len, const int* kv_len, const int* tile_req,
+                                       const int* tile_tok0, int n_tiles, int nq, int nkv, int d, int dv,
+                                       float scale, int window, int dtype, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (d <= 0 || d > 256 || dv <= 0 || dv > 256)
+    MI_REFUSE("attention: head sizes %d (keys) and %d (values) must lie in [1, 256]", d, dv);
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0)
+    MI_REFUSE("attention: %d query heads cannot share %d key/value heads", nq, nkv);
+  if ((long long)n_tiles * nq > 0x7fffffffLL) MI_REFUSE("attention: too many blocks for one launch");
+  if (page_size <= 0 || window < 0) MI_REFUSE("attention: bad page size %d or window %d", page_size, window);
+  if (!mi_aligned(kcache, 16) || !mi_aligned(vcache, 16)) MI_REFUSE("attention: cache must be 16-byte aligned");
+  int rc;
+#define MI_GO(T, DMAX)                                                                              \
+  rc = launch<T, DMAX>(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride,        \
+                       table_rows, page_size, q_start, q_len, kv_len, tile_req, tile_tok0, n_tiles, nq, nkv, d, dv, \
+                       scale, window, stream)
+  if (dtype == MI_DTYPE_F32) {
+    if (dv <= 64) MI_GO(float, 64);
+    else if (dv <= 128) MI_GO(float, 128);
+    else MI_GO(float, 256);
+  } else if (dtype == MI_DTYPE_BF16) {
+    if (dv <= 64) MI_GO(bf16, 64);
+    else if (dv <= 128) MI_GO(bf16, 128);
+    else MI_GO(bf16, 256);
+  } else {
+    MI_REFUSE("attention: unknown dtype %d", dtype);
+  }
+#undef MI_GO
+  if (rc) return rc;
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// keys and values of one size, a multiple of 16 (what the tensor-core kernels take as well)
 extern "C" int mi_attention_generic(const void* q, int q_stride, void* out, int out_stride,
                                     const void* kcache, const void* vcache, const int* block_table,
                                     int bt_stride, const int* table_rows, int page_size, const int* q_start,
@@ -191,28 +258,7 @@ extern "C" int mi_attention_generic(const void* q, int q_stride, void* out, int 
   if (n_tiles <= 0) return 0;
   if (d <= 0 || d % 16 != 0 || d > 256)
     MI_REFUSE("attention: head size %d is not a multiple of 16 in [16, 256]", d);
-  if (nq <= 0 || nkv <= 0 || nq % nkv != 0)
-    MI_REFUSE("attention: %d query heads cannot share %d key/value heads", nq, nkv);
-  if ((long long)n_tiles * nq > 0x7fffffffLL) MI_REFUSE("attention: too many blocks for one launch");
-  if (page_size <= 0 || window < 0) MI_REFUSE("attention: bad page size %d or window %d", page_size, window);
-  if (!mi_aligned(kcache, 16) || !mi_aligned(vcache, 16)) MI_REFUSE("attention: cache must be 16-byte aligned");
-  int rc;
-#define MI_GO(T, DMAX)                                                                              \
-  rc = launch<T, DMAX>(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride,        \
-                       table_rows, page_size, q_start, q_len, kv_len, tile_req, tile_tok0, n_tiles, nq, nkv, d, \
-                       scale, window, stream)
-  if (dtype == MI_DTYPE_F32) {
-    if (d <= 64) MI_GO(float, 64);
-    else if (d <= 128) MI_GO(float, 128);
-    else MI_GO(float, 256);
-  } else if (dtype == MI_DTYPE_BF16) {
-    if (d <= 64) MI_GO(bf16, 64);
-    else if (d <= 128) MI_GO(bf16, 128);
-    else MI_GO(bf16, 256);
-  } else {
-    MI_REFUSE("attention: unknown dtype %d", dtype);
-  }
-#undef MI_GO
-  if (rc) return rc;
-  MI_RETURN_LAUNCH_STATUS();
+  return mi_attention_generic_kv(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride, table_rows,
+                                 page_size, q_start, q_len, kv_len, tile_req, tile_tok0, n_tiles, nq, nkv, d, d,
+                                 scale, window, dtype, stream);
 }

@@ -38,6 +38,10 @@ LIBRARIES: dict[str, tuple[list[str], list[str], list[str]]] = {
     "attention_mma": (["attention_mma.cu"], ["common.cuh", "attention_noalloc.h"], []),
     "gemm_tma": (["gemm_tma.cu"], ["common.cuh"], []),
     "attention_tc": (["attention_tc.cu"], ["common.cuh"], []),
+    "layernorm": (["layernorm.cu"], ["common.cuh"], []),
+    "rope_norm": (["rope_norm.cu"], ["common.cuh"], []),
+    "recurrent": (["recurrent.cu"], ["common.cuh"], []),
+    "moe": (["moe.cu"], ["common.cuh"], []),
 }
 
 

@@ -177,6 +177,10 @@ __host__ __device__ inline int mi_swizzle_mask(int d, int elem_size) {
   if (n < 2 || (n & (n - 1))) return 0;
   return (n < 8 ? n : 8) - 1;
 }
+// The same for rows of any size: a row that is no whole number of 16-byte chunks is stored as it is.
+__host__ __device__ inline int mi_swizzle_mask_rows(int d, int elem_size) {
+  return (d * elem_size) % 16 ? 0 : mi_swizzle_mask(d, elem_size);
+}
 // Physical element index within a row of logical element k (epc = elements per 16-byte chunk).
 __device__ __forceinline__ int mi_swizzled(int k, int t, int mask, int epc) {
   return (((k / epc) ^ (t & mask)) * epc) + (k % epc);

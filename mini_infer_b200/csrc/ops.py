@@ -144,6 +144,10 @@ def _sig_attention_generic(lib: ctypes.CDLL) -> None:
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
         c_float, c_int, c_int, c_void_p]
     lib.mi_attention_generic_tile_tokens.restype = c_int
+    lib.mi_attention_generic_kv.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+        c_float, c_int, c_int, c_void_p]
 
 
 def _sig_sampling(lib: ctypes.CDLL) -> None:
@@ -200,7 +204,54 @@ def _sig_attention_tc(lib: ctypes.CDLL) -> None:
     lib.mi_set_status_word.argtypes = [c_void_p]
 
 
+def _sig_layernorm(lib: ctypes.CDLL) -> None:
+    lib.mi_embedding_scaled.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]
+    lib.mi_add_layernorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
+
+
+def _sig_rope_norm(lib: ctypes.CDLL) -> None:
+    lib.mi_rope_norm_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                       c_int, c_int, c_void_p]
+    lib.mi_gate_mul.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                c_int, c_void_p]
+
+
+def _sig_recurrent(lib: ctypes.CDLL) -> None:
+    ll = ctypes.c_longlong
+    lib.mi_causal_conv.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, ll, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    lib.mi_rglru_scan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int,
+                                  c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, ll, c_int,
+                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    lib.mi_gla_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
+                                c_void_p, ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                c_int, c_int, c_void_p]
+    lib.mi_headnorm_gate.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                     c_int, c_float, c_int, c_float, c_int, c_void_p]
+
+
+def _sig_moe(lib: ctypes.CDLL) -> None:
+    ll = ctypes.c_longlong
+    lib.mi_moe_route.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                 c_void_p]
+    lib.mi_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.mi_moe_tile_rows.restype = c_int
+    lib.mi_moe_gate_up.argtypes = [c_void_p, c_int, c_void_p, c_void_p, ll, c_void_p, c_int, c_void_p, c_int,
+                                   c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]
+    lib.mi_moe_down.argtypes = [c_void_p, c_void_p, ll, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                c_void_p]
+    lib.mi_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                   c_int, c_void_p]
+    lib.mi_clamped_glu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]
+
+
 _SIGNATURES = {
+    "layernorm": _sig_layernorm,
+    "rope_norm": _sig_rope_norm,
+    "recurrent": _sig_recurrent,
+    "moe": _sig_moe,
     "attention_tc": _sig_attention_tc,
     "gemm_tma": _sig_gemm_tma,
     "attention_mma": _sig_attention_mma,
@@ -993,3 +1044,378 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     if _MM_OUT_DTYPE:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t()).float()
+
+
+# --------------------------------------------------------------------------------------- layer norm
+
+
+def embedding_scaled(table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.Tensor:
+    """``float(table[ids]) * scale`` as the fp32 residual stream ``[M, H]``."""
+    _cuda(table, ids)
+    if ids.dtype != torch.int32 or ids.dim() != 1 or not ids.is_contiguous():
+        raise KernelError("embedding: ids must be a contiguous int32 vector")
+    if table.dim() != 2 or not table.is_contiguous():
+        raise KernelError("embedding: table must be a contiguous [V, H] matrix")
+    V, H = table.shape
+    out = torch.empty((ids.shape[0], H), dtype=torch.float32, device=table.device)
+    lib = _lib("layernorm")
+    rc = lib.mi_embedding_scaled(_ptr(table), _ptr(ids), _ptr(out), ids.shape[0], H, V, float(scale),
+                                 _code(table.dtype), _stream())
+    _finish(lib, rc, "embedding")
+    return out
+
+
+def add_layernorm(stream: torch.Tensor, adds, norms, eps: float, dtype: torch.dtype, *,
+                  rows: torch.Tensor | None = None, update_stream: bool = True):
+    """Layer norm(s) of ``r = stream + sum(adds)`` (fp32; ``adds``: up to two ``[M, H]`` tensors
+    of ``dtype``).  ``norms``: one or two ``(gain, bias)`` pairs (fp32 ``[H]``); one output in
+    ``dtype`` per pair.  Without ``rows`` and with ``update_stream`` the stream is replaced by
+    ``r`` in place; with ``rows`` (int32) only those rows are normalised and the stream stays."""
+    adds = [a for a in adds if a is not None]
+    if len(adds) > 2 or not 1 <= len(norms) <= 2:
+        raise KernelError("layernorm: at most two addends and one or two norms")
+    _cuda(stream, rows, *adds)
+    if stream.dtype != torch.float32 or stream.dim() != 2 or not stream.is_contiguous():
+        raise KernelError("layernorm: the stream must be a contiguous fp32 [M, H] matrix")
+    H = stream.shape[1]
+    for a in adds:
+        if a.shape != stream.shape or a.dtype != dtype or not a.is_contiguous():
+            raise KernelError("layernorm: addends must be contiguous, shaped like the stream, in the compute dtype")
+    for w, b in norms:
+        for t in (w, b):
+            if t.dtype != torch.float32 or t.shape != (H,) or not t.is_contiguous():
+                raise KernelError(f"layernorm: gains and biases must be fp32 [{H}]")
+    if rows is not None and (rows.dtype != torch.int32 or rows.dim() != 1 or not rows.is_contiguous()):
+        raise KernelError("layernorm: rows must be a contiguous int32 vector")
+    M = stream.shape[0] if rows is None else rows.shape[0]
+    outs = [torch.empty((M, H), dtype=dtype, device=stream.device) for _ in norms]
+    a1 = adds[0] if adds else None
+    a2 = adds[1] if len(adds) > 1 else None
+    w2, b2 = norms[1] if len(norms) > 1 else (None, None)
+    lib = _lib("layernorm")
+    rc = lib.mi_add_layernorm(_ptr(stream), _ptr(a1), _ptr(a2),
+                              _ptr(stream if (rows is None and update_stream and adds) else None), _ptr(rows),
+                              _ptr(norms[0][0]), _ptr(norms[0][1]), _ptr(outs[0]), _ptr(w2), _ptr(b2),
+                              _ptr(outs[1] if len(outs) > 1 else None), M, H, float(eps), _code(dtype), _stream())
+    _finish(lib, rc, "layernorm")
+    return outs
+
+
+# --------------------------------------------------------------------------------------- rotation, unit norm, gates
+
+
+def _cols(t: torch.Tensor, what: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{what}: needs a [tokens, columns] tensor (or column range) with unit inner stride")
+
+
+def rope_norm_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int, nq: int, nkv: int, d: int, dv: int, *,
+                    positions: torch.Tensor | None, inv_freq: torch.Tensor | None, rot: int, unit_norm: bool,
+                    eps: float, slots: torch.Tensor | None = None, kcache: torch.Tensor | None = None,
+                    vcache: torch.Tensor | None = None) -> None:
+    """In the packed projection ``[M, stride]`` (q at columns ``q_off``, ``nq`` heads of ``d``; k at
+    ``k_off``, ``nkv`` heads of ``d``; v at ``v_off``, ``nkv`` heads of ``dv``): rotate q and k on their
+    first ``rot`` dimensions (interleaved pairs, fp32 angles ``position * inv_freq[i]``), divide
+    them by their root mean square over the head (``unit_norm``), write q and k back in place and
+    store k and v at ``slots`` of the caches ``[pages, nkv, page_size, d | dv]``."""
+    _cuda(packed, positions, inv_freq, slots, kcache, vcache)
+    _cols(packed, "rope_norm")
+    M, width = packed.shape
+    if q_off + nq * d > width or k_off + nkv * d > width or v_off + nkv * dv > width:
+        raise KernelError("rope_norm: a column range lies outside the packed projection")
+    if rot:
+        if positions is None or positions.dtype != torch.int32 or positions.shape != (M,):
+            raise KernelError("rope_norm: positions must be int32 [M]")
+        if inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.shape != (rot // 2,) or not inv_freq.is_contiguous():
+            raise KernelError("rope_norm: inv_freq must be fp32 [rot / 2]")
+    writes = kcache is not None
+    page_size = 0
+    if writes:
+        if slots is None or slots.dtype != torch.int32 or slots.shape != (M,):
+            raise KernelError("rope_norm: slots must be int32 [M]")
+        for c, size in ((kcache, d), (vcache, dv)):
+            if (c is None or c.dtype != packed.dtype or c.dim() != 4 or c.shape[1] != nkv or c.shape[3] != size
+                    or not c.is_contiguous()):
+                raise KernelError("rope_norm: caches must be contiguous [pages, nkv, page_size, size] in the packed dtype")
+        page_size = int(kcache.shape[2])
+        if vcache.shape[2] != page_size:
+            raise KernelError("rope_norm: key and value pages differ in size")
+    lib = _lib("rope_norm")
+    rc = lib.mi_rope_norm_store(_ptr(packed), packed.stride(0), q_off, k_off, v_off, _ptr(positions), _ptr(inv_freq),
+                                _ptr(slots), _ptr(kcache), _ptr(vcache), M, nq, nkv, d, dv, int(rot),
+                                1 if unit_norm else 0, float(eps), page_size, 1 if writes else 0,
+                                _code(packed.dtype), _stream())
+    _finish(lib, rc, "rope_norm")
+
+
+_ACT = {"sigmoid": 1, "silu": 2, None: 0}
+
+
+def gate_mul(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, act: str, scale: float = 1.0) -> None:
+    """``out = x * act(gate) * scale`` element by element; all three ``[M, C]`` (column ranges of
+    wider tensors are fine), ``act`` ``"sigmoid"`` or ``"silu"``, fp32 arithmetic."""
+    _cuda(x, gate, out)
+    for t in (x, gate, out):
+        _cols(t, "gate_mul")
+    if x.shape != gate.shape or x.shape != out.shape or not (x.dtype == gate.dtype == out.dtype):
+        raise KernelError("gate_mul: x, gate and out must agree in shape and dtype")
+    lib = _lib("rope_norm")
+    rc = lib.mi_gate_mul(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _ptr(out), out.stride(0), x.shape[0],
+                         x.shape[1], _ACT[act], float(scale), _code(x.dtype), _stream())
+    _finish(lib, rc, "gate_mul")
+
+
+def attention_kv(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: int, d: int, dv: int, scale: float,
+                 window: int = 0) -> None:
+    """Attention of this step's queries over one cache layer whose keys (size ``d``) and values
+    (size ``dv``) may differ in size: the CUDA-core kernel with fp32 scores, weights and sums, for
+    float32 and bfloat16 alike.  ``q`` and ``out`` are ``[M, nq * d]`` / ``[M, nq * dv]`` column ranges."""
+    group = ctx.groups[cache.group]
+    _cuda(q, out, cache.k, cache.v)
+    _cols(q, "attention")
+    _cols(out, "attention")
+    if q.shape[1] != nq * d or out.shape[1] != nq * dv or q.dtype != out.dtype:
+        raise KernelError("attention: q must be [M, nq * d] and out [M, nq * dv] in one dtype")
+    kc, vc = cache.k, cache.v
+    if (kc.dtype != q.dtype or vc.dtype != q.dtype or kc.dim() != 4 or vc.dim() != 4
+            or kc.shape[1:] != (nkv, group.page_size, d) or vc.shape[1:] != (nkv, group.page_size, dv)
+            or not kc.is_contiguous() or not vc.is_contiguous()):
+        raise KernelError("attention: caches must be contiguous [pages, nkv, page_size, d | dv] in q's dtype")
+    tile_req, tile_tok0, n_tiles = ctx.q_tiles(ATTENTION_TILE_TOKENS)
+    lib = _lib("attention_generic")
+    if lib.mi_attention_generic_tile_tokens() != ATTENTION_TILE_TOKENS:
+        raise KernelError("attention: the kernel's tile size differs from ATTENTION_TILE_TOKENS")
+    bt = group.block_table
+    rc = lib.mi_attention_generic_kv(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kc), _ptr(vc), _ptr(bt), bt.stride(0),
+        _ptr(group.table_rows), int(group.page_size), _ptr(ctx.q_start), _ptr(ctx.q_len), _ptr(ctx.kv_len),
+        _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), nq, nkv, d, dv, float(scale), int(window),
+        _code(q.dtype), _stream())
+    _finish(lib, rc, "attention")
+
+
+# --------------------------------------------------------------------------------------- recurrences
+
+
+def _state_rows(state: torch.Tensor, what: str) -> int:
+    if state.dtype != torch.float32 or state.dim() < 2 or not state.is_contiguous():
+        raise KernelError(f"{what}: the state arena must be contiguous fp32 [slots, ...]")
+    return state.stride(0)
+
+
+def _f32vec(t: torch.Tensor | None, n: int, what: str) -> None:
+    if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+        raise KernelError(f"{what}: needs a contiguous fp32 tensor of {n} elements")
+
+
+def causal_conv(x: torch.Tensor, x_bias: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor | None,
+                state: torch.Tensor, ctx, out: torch.Tensor) -> None:
+    """Per channel ``out[t] = bias + sum_j weight[:, j] * in[t - (taps - 1 - j)]`` with ``in = x +
+    x_bias``; the ``taps - 1`` inputs before a request's portion come from the head of its state
+    row (``[taps - 1, C]``, oldest first; zeros at the start of a sequence).  The state is read
+    only (``rglru_scan`` moves it on)."""
+    _cuda(x, x_bias, weight, bias, state, out)
+    _cols(x, "causal_conv")
+    _cols(out, "causal_conv")
+    C = x.shape[1]
+    if weight.dtype != torch.float32 or weight.dim() != 2 or weight.shape[0] != C or not weight.is_contiguous():
+        raise KernelError("causal_conv: the taps must be contiguous fp32 [C, taps]")
+    taps = weight.shape[1]
+    _f32vec(x_bias, C, "causal_conv")
+    _f32vec(bias, C, "causal_conv")
+    stride = _state_rows(state, "causal_conv")
+    if stride < (taps - 1) * C or out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("causal_conv: state row too short, or out does not match x")
+    lib = _lib("recurrent")
+    rc = lib.mi_causal_conv(_ptr(x), x.stride(0), _ptr(x_bias), _ptr(weight), _ptr(bias), _ptr(state), stride,
+                            _ptr(ctx.q_start), _ptr(ctx.q_len), _ptr(ctx.state_slot), _ptr(out), out.stride(0),
+                            ctx.n_requests, _max_q_len(ctx), C, taps, _code(x.dtype), _stream())
+    _finish(lib, rc, "causal_conv")
+
+
+def _max_q_len(ctx) -> int:
+    return 1 if ctx.decode_only else max(ctx.host_q_len)
+
+
+def rglru_scan(gates: torch.Tensor, gate_bias_r: torch.Tensor, gate_bias_i: torch.Tensor, lam: torch.Tensor,
+               decay_scale: float, u: torch.Tensor, y: torch.Tensor, y_bias: torch.Tensor | None,
+               x_in: torch.Tensor, x_in_bias: torch.Tensor | None, taps: int, state: torch.Tensor, ctx,
+               out: torch.Tensor) -> None:
+    """The real-gated linear recurrent unit over each request's portion, from and into its state
+    row ``[taps - 1 + 1, C]`` (the convolution's last inputs, then the recurrent state):
+    ``r = sigmoid(g_r + b_r)``, ``i = sigmoid(g_i + b_i)``, ``log a = -decay_scale * r * softplus(lam)``,
+    ``S = a S + sqrt(1 - a^2) * i * u``, ``out = S * gelu_tanh(y + y_bias)``.  ``gates`` is fp32
+    ``[blocks, M, 2 * bw]`` (per block of ``bw`` channels the ``r`` then the ``i`` pre-activations)."""
+    _cuda(gates, gate_bias_r, gate_bias_i, lam, u, y, y_bias, x_in, x_in_bias, state, out)
+    for t in (u, y, x_in, out):
+        _cols(t, "rglru")
+    M, C = u.shape
+    if gates.dtype != torch.float32 or gates.dim() != 3 or gates.shape[1] != M or not gates.is_contiguous():
+        raise KernelError("rglru: gates must be contiguous fp32 [blocks, M, 2 * bw]")
+    bw = gates.shape[2] // 2
+    if gates.shape[0] * bw != C:
+        raise KernelError("rglru: blocks * bw must equal the channel count")
+    for t in (gate_bias_r, gate_bias_i, lam):
+        _f32vec(t, C, "rglru")
+    _f32vec(y_bias, C, "rglru")
+    _f32vec(x_in_bias, C, "rglru")
+    stride = _state_rows(state, "rglru")
+    if stride < taps * C:
+        raise KernelError("rglru: state row too short")
+    lib = _lib("recurrent")
+    rc = lib.mi_rglru_scan(_ptr(gates), M, bw, _ptr(gate_bias_r), _ptr(gate_bias_i), _ptr(lam), float(decay_scale),
+                           _ptr(u), u.stride(0), _ptr(y), y.stride(0), _ptr(y_bias), _ptr(x_in), x_in.stride(0),
+                           _ptr(x_in_bias), _ptr(state), stride, int(taps), _ptr(ctx.q_start), _ptr(ctx.q_len),
+                           _ptr(ctx.state_slot), _ptr(out), out.stride(0), ctx.n_requests, C, _code(u.dtype), _stream())
+    _finish(lib, rc, "rglru")
+
+
+def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias: torch.Tensor | None,
+             tau: float, q_scale: float, heads: int, dk: int, dv: int, state: torch.Tensor, ctx) -> torch.Tensor:
+    """Gated linear attention over each request's portion, from and into its state row
+    ``[heads, dk, dv]``: ``S = diag(alpha) S + k v^T``, ``o = S^T (q * q_scale)`` with
+    ``alpha = sigmoid(z + z_bias)^(1 / tau)``.  q, k, v: column ranges of one packed projection;
+    ``z`` fp32 ``[M, heads * dk]``.  Returns fp32 ``o [M, heads * dv]``."""
+    _cuda(q, k, v, z, z_bias, state)
+    for t in (q, k, v, z):
+        _cols(t, "gla")
+    M = q.shape[0]
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or not (q.dtype == k.dtype == v.dtype):
+        raise KernelError("gla: q, k and v must be column ranges of one packed projection")
+    if q.shape[1] != heads * dk or k.shape[1] != heads * dk or v.shape[1] != heads * dv:
+        raise KernelError("gla: q, k must be [M, heads * dk] and v [M, heads * dv]")
+    if z.dtype != torch.float32 or z.shape != (M, heads * dk):
+        raise KernelError("gla: z must be fp32 [M, heads * dk]")
+    _f32vec(z_bias, heads * dk, "gla")
+    stride = _state_rows(state, "gla")
+    if stride < heads * dk * dv:
+        raise KernelError("gla: state row too short")
+    o = torch.empty((M, heads * dv), dtype=torch.float32, device=q.device)
+    lib = _lib("recurrent")
+    rc = lib.mi_gla_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(z), z.stride(0), _ptr(z_bias), 1.0 / float(tau),
+                         float(q_scale), _ptr(state), stride, _ptr(ctx.q_start), _ptr(ctx.q_len),
+                         _ptr(ctx.state_slot), _ptr(o), o.stride(0), ctx.n_requests, heads, dk, dv, _code(q.dtype),
+                         _stream())
+    _finish(lib, rc, "gla")
+    return o
+
+
+def headnorm_gate(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor, heads: int,
+                  dv: int, eps: float, act: str | None, scale: float = 1.0) -> None:
+    """``out = o / sqrt(mean_head(o^2) + eps) * weight * act(gate) * scale`` per head of ``dv``
+    (``o`` fp32 ``[M, heads * dv]``, ``weight`` fp32 ``[dv]``, ``gate`` and ``out`` in the compute dtype)."""
+    _cuda(o, weight, gate, out)
+    _cols(o, "headnorm_gate")
+    _cols(out, "headnorm_gate")
+    if o.dtype != torch.float32 or o.shape[1] != heads * dv or out.shape != o.shape:
+        raise KernelError("headnorm_gate: o must be fp32 [M, heads * dv] and out shaped like it")
+    _f32vec(weight, dv, "headnorm_gate")
+    if gate is not None:
+        _cols(gate, "headnorm_gate")
+        if gate.shape != o.shape or gate.dtype != out.dtype:
+            raise KernelError("headnorm_gate: the gate must match out")
+    lib = _lib("recurrent")
+    rc = lib.mi_headnorm_gate(_ptr(o), o.stride(0), _ptr(weight), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                              _ptr(out), out.stride(0), o.shape[0], heads, dv, float(eps),
+                              _ACT[act if gate is not None else None], float(scale), _code(out.dtype), _stream())
+    _finish(lib, rc, "headnorm_gate")
+
+
+# --------------------------------------------------------------------------------------- routed experts
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, top: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 router logits ``x router^T``; per token the ``top`` experts with the largest logits
+    (int32 ``[M, top]``, largest first) and the softmax over those logits alone (fp32)."""
+    _cuda(x, router)
+    _cols(x, "moe")
+    if router.dim() != 2 or router.shape[1] != x.shape[1] or router.dtype != x.dtype or not router.is_contiguous():
+        raise KernelError("moe: the router must be a contiguous [experts, H] matrix in x's dtype")
+    M, H = x.shape
+    E = router.shape[0]
+    ids = torch.empty((M, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((M, top), dtype=torch.float32, device=x.device)
+    lib = _lib("moe")
+    rc = lib.mi_moe_route(_ptr(x), x.stride(0), _ptr(router), _ptr(ids), _ptr(weights), M, H, E, int(top),
+                          _code(x.dtype), _stream())
+    _finish(lib, rc, "moe_route")
+    return ids, weights
+
+
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                w_down: torch.Tensor, limit: float, alpha: float, shared: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[t] = sum_k weights[t, k] * expert_{ids[t, k]}(x[t]) (+ shared[t])`` with
+    ``expert(x) = W_down glu(W_gate x, W_up x)``, ``glu(g, u) = g' sigmoid(alpha g') (u' + 1)``,
+    ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``.  Weights are stacked per expert:
+    ``w_gate, w_up [E, ff, H]``, ``w_down [E, H, ff]``.  Entries are sorted by expert on the
+    device and the products walk tiles of one expert's rows; nothing is read back."""
+    _cuda(x, ids, weights, w_gate, w_up, w_down, shared)
+    _cols(x, "moe")
+    M, H = x.shape
+    E, ff, _ = w_gate.shape
+    top = ids.shape[1]
+    for w, shape in ((w_gate, (E, ff, H)), (w_up, (E, ff, H)), (w_down, (E, H, ff))):
+        if tuple(w.shape) != shape or w.dtype != x.dtype or not w.is_contiguous():
+            raise KernelError("moe: expert weights must be contiguous [E, ff, H], [E, ff, H], [E, H, ff] in x's dtype")
+    if ids.dtype != torch.int32 or weights.dtype != torch.float32 or ids.shape != weights.shape or ids.shape[0] != M \
+            or not ids.is_contiguous() or not weights.is_contiguous():
+        raise KernelError("moe: ids int32 [M, top] and weights fp32 [M, top]")
+    if shared is not None:
+        _cols(shared, "moe")
+        if shared.shape != (M, H) or shared.dtype != x.dtype:
+            raise KernelError("moe: the shared expert's output must be [M, H] in x's dtype")
+    n = M * top
+    lib = _lib("moe")
+    tile = lib.mi_moe_tile_rows()
+    dev = x.device
+    perm = torch.empty(n, dtype=torch.int32, device=dev)
+    inv = torch.empty(n, dtype=torch.int32, device=dev)
+    plan = torch.empty(2 + E + 3 * (-(-n // tile) + E), dtype=torch.int32, device=dev)
+    rc = lib.mi_moe_plan(_ptr(ids), n, E, _ptr(perm), _ptr(inv), _ptr(plan), _stream())
+    _finish(lib, rc, "moe_plan")
+    act = torch.empty((n, ff), dtype=x.dtype, device=dev)
+    rc = lib.mi_moe_gate_up(_ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), ff * H, _ptr(perm), top, _ptr(plan), E,
+                            _ptr(act), n, ff, H, float(limit), float(alpha), _code(x.dtype), _stream())
+    _finish(lib, rc, "moe_gate_up")
+    y = torch.empty((n, H), dtype=torch.float32, device=dev)
+    rc = lib.mi_moe_down(_ptr(act), _ptr(w_down), H * ff, _ptr(plan), E, _ptr(y), n, H, ff, _code(x.dtype), _stream())
+    _finish(lib, rc, "moe_down")
+    out = torch.empty((M, H), dtype=x.dtype, device=dev)
+    rc = lib.mi_moe_combine(_ptr(y), _ptr(inv), _ptr(weights), _ptr(shared), shared.stride(0) if shared is not None else 0,
+                            _ptr(out), M, H, top, _code(x.dtype), _stream())
+    _finish(lib, rc, "moe_combine")
+    return out
+
+
+def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """``glu(gate_up[:, :I], gate_up[:, I:])`` of ``moe_experts`` for a dense expert."""
+    _cuda(gate_up)
+    _cols(gate_up, "clamped_glu")
+    M, I2 = gate_up.shape
+    out = torch.empty((M, I2 // 2), dtype=gate_up.dtype, device=gate_up.device)
+    lib = _lib("moe")
+    rc = lib.mi_clamped_glu(_ptr(gate_up), gate_up.stride(0), _ptr(out), M, I2 // 2, float(limit), float(alpha),
+                            _code(gate_up.dtype), _stream())
+    _finish(lib, rc, "clamped_glu")
+    return out
+
+
+def block_diagonal_gates(u: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``gates[b] = u[:, b * bw:(b + 1) * bw] @ w[b]^T`` in fp32 for ``w [blocks, n, bw]``: float32
+    through the true-fp32 product block by block, bfloat16 through the library's batched product
+    with fp32 output.  Returns fp32 ``[blocks, M, n]``."""
+    global launch_count
+    _cuda(u, w)
+    _cols(u, "block_diagonal")
+    blocks, n, bw = w.shape
+    M = u.shape[0]
+    if u.shape[1] != blocks * bw or w.dtype != u.dtype or not w.is_contiguous():
+        raise KernelError("block_diagonal: u must be [M, blocks * bw] and w contiguous [blocks, n, bw] in u's dtype")
+    if u.dtype == torch.float32:
+        out = torch.empty((blocks, M, n), dtype=torch.float32, device=u.device)
+        for b in range(blocks):
+            gemm_f32(u[:, b * bw:(b + 1) * bw], w[b], out[b])
+        return out
+    launch_count += 1
+    ub = u.unflatten(1, (blocks, bw)).transpose(0, 1)           # [blocks, M, bw], a view
+    return torch.bmm(ub, w.transpose(1, 2), out_dtype=torch.float32)

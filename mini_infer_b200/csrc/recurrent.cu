@@ -1,0 +1,323 @@
+// Mixers that carry a state of fixed size from token to token instead of keys and values.
+//
+// Every request of a step brings q_len[b] consecutive tokens (rows q_start[b] .. of the packed
+// activations) and owns row state_slot[b] of a state arena (fp32, zeroed when the request is
+// admitted).  All recurrences run in fp32, token by token in the order of the positions, so a
+// result never depends on how a prompt was cut into steps or on what else is in the batch.
+//
+//   mi_causal_conv     per channel: out[t] = b + sum_j w[j] * in[t - (taps-1-j)], in = x + x_bias,
+//                      with the taps-1 inputs before the portion taken from the state (zeros before
+//                      the start of a sequence).  Does not change the state.
+//   mi_rglru_scan      the real-gated linear recurrent unit:
+//                        r = sigmoid(gr + br), i = sigmoid(gi + bi), log a = -c * r * softplus(lam),
+//                        S = a S + sqrt(1 - a^2) * i * u;   out = T(S * gelu_tanh(y + by))
+//                      and, for the convolution in front of it, the new last taps-1 inputs.
+//   mi_gla_scan        gated linear attention, per head: S = diag(alpha) S + k v^T, o = S^T (q * qscale),
+//                      alpha = sigmoid(z + bz)^(1/tau).
+//   mi_headnorm_gate   out = T(o / sqrt(mean_head(o^2) + eps) * w * act(g) * scale) per head of dv.
+#include "common.cuh"
+
+MI_DEFINE_ERROR_API()
+
+#define MAX_TAPS 16
+
+// ------------------------------------------------------------------------------------------
+// causal convolution over a portion, with the state's tail in front of it
+// state row of a request: [taps-1][C] inputs (oldest first), then whatever else the mixer keeps
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void causal_conv_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ x_bias,
+                                   const float* __restrict__ w, const float* __restrict__ b,
+                                   const float* __restrict__ state, long long state_stride,
+                                   const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                   const int* __restrict__ state_slot, T* __restrict__ out, int out_stride,
+                                   int C, int taps, int tile) {
+  mi_pdl_enter();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int req = blockIdx.z;
+  const int len = q_len[req];
+  const int t0 = blockIdx.y * tile;
+  if (c >= C || t0 >= len) return;
+  const int row0 = q_start[req];
+  const float* tail = state + (size_t)state_slot[req] * state_stride;
+  float wv[MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) wv[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+  const float xb = x_bias ? x_bias[c] : 0.f, bias = b ? b[c] : 0.f;
+  const int t1 = min(len, t0 + tile);
+  for (int t = t0; t < t1; ++t) {
+    float acc = bias;
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j) {
+      if (j < taps) {
+        const int src = t - (taps - 1 - j);
+        const float v = src >= 0 ? mi_to_float(x[(size_t)(row0 + src) * x_stride + c]) + xb
+                                 : tail[(size_t)(taps - 1 + src) * C + c];
+        acc = fmaf(wv[j], v, acc);
+      }
+    }
+    out[(size_t)(row0 + t) * out_stride + c] = mi_from_float<T>(acc);
+  }
+}
+
+extern "C" int mi_causal_conv(const void* x, int x_stride, const float* x_bias, const float* w, const float* b,
+                              const float* state, long long state_stride, const int* q_start, const int* q_len,
+                              const int* state_slot, void* out, int out_stride, int n_requests, int max_q_len,
+                              int C, int taps, int dtype, cudaStream_t stream) {
+  if (n_requests <= 0 || max_q_len <= 0) return 0;
+  if (taps < 1 || taps > MAX_TAPS) MI_REFUSE("causal_conv: %d taps (1 to %d are taken)", taps, MAX_TAPS);
+  const int tile = 16;
+  dim3 grid((C + 127) / 128, (max_q_len + tile - 1) / tile, n_requests);
+  if (grid.y > 65535 || grid.z > 65535) MI_REFUSE("causal_conv: too many tiles for one launch");
+  if (dtype == MI_DTYPE_F32)
+    MI_LAUNCH((causal_conv_kernel<float>), grid, 128, 0, stream, (const float*)x, x_stride, x_bias, w, b, state,
+              state_stride, q_start, q_len, state_slot, (float*)out, out_stride, C, taps, tile);
+  else if (dtype == MI_DTYPE_BF16)
+    MI_LAUNCH((causal_conv_kernel<bf16>), grid, 128, 0, stream, (const bf16*)x, x_stride, x_bias, w, b, state,
+              state_stride, q_start, q_len, state_slot, (bf16*)out, out_stride, C, taps, tile);
+  else
+    MI_REFUSE("causal_conv: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------------------------------
+// real-gated linear recurrent unit.  One thread per (request, channel) walks the portion.
+// gates [blocks][M][2 * bw]: for block k, row m: the r pre-activations of its bw channels, then the i ones.
+// state row: [taps-1][C] convolution inputs, then [C] the recurrent state.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float mi_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float mi_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float mi_gelu_tanh(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void rglru_scan_kernel(const float* __restrict__ gates, int M, int bw,
+                                  const float* __restrict__ br, const float* __restrict__ bi,
+                                  const float* __restrict__ lam, float decay_scale,
+                                  const T* __restrict__ u, int u_stride,
+                                  const T* __restrict__ y, int y_stride, const float* __restrict__ y_bias,
+                                  const T* __restrict__ xin, int xin_stride, const float* __restrict__ xin_bias,
+                                  float* __restrict__ state, long long state_stride, int taps,
+                                  const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                  const int* __restrict__ state_slot, T* __restrict__ out, int out_stride, int C) {
+  mi_pdl_enter();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int req = blockIdx.y;
+  if (c >= C) return;
+  const int len = q_len[req], row0 = q_start[req];
+  float* st = state + (size_t)state_slot[req] * state_stride;
+  float* Sp = st + (size_t)(taps - 1) * C + c;
+  float S = *Sp;
+  const int blk = c / bw, cj = c - blk * bw;
+  const float* g = gates + ((size_t)blk * M + row0) * (2 * bw) + cj;
+  const float vbr = br[c], vbi = bi[c], yb = y_bias ? y_bias[c] : 0.f;
+  const float sp = decay_scale * mi_softplus(lam[c]);
+  for (int t = 0; t < len; ++t) {
+    const float r = mi_sigmoid(g[0] + vbr), ig = mi_sigmoid(g[bw] + vbi);
+    g += 2 * bw;
+    const float log_a = -sp * r;
+    const float a = expf(log_a);
+    const float mult = sqrtf(-expm1f(2.f * log_a));
+    const float uv = mi_to_float(u[(size_t)(row0 + t) * u_stride + c]);
+    S = fmaf(a, S, mult * (ig * uv));
+    const float yv = mi_gelu_tanh(mi_to_float(y[(size_t)(row0 + t) * y_stride + c]) + yb);
+    out[(size_t)(row0 + t) * out_stride + c] = mi_from_float<T>(S * yv);
+  }
+  *Sp = S;
+  // the convolution's next tail: the last taps-1 of (old tail, this portion's inputs)
+  if (taps > 1) {
+    const float xb = xin_bias ? xin_bias[c] : 0.f;
+    float keep[MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j) {
+      if (j < taps - 1) {
+        const int src = len - (taps - 1) + j;   // portion offset of the j-th kept input
+        keep[j] = src >= 0 ? mi_to_float(xin[(size_t)(row0 + src) * xin_stride + c]) + xb
+                           : st[(size_t)(taps - 1 + src) * C + c];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j)
+      if (j < taps - 1) st[(size_t)j * C + c] = keep[j];
+  }
+}
+
+extern "C" int mi_rglru_scan(const float* gates, int M, int bw, const float* br, const float* bi, const float* lam,
+                             float decay_scale, const void* u, int u_stride, const void* y, int y_stride,
+                             const float* y_bias, const void* xin, int xin_stride, const float* xin_bias,
+                             float* state, long long state_stride, int taps, const int* q_start, const int* q_len,
+                             const int* state_slot, void* out, int out_stride, int n_requests, int C, int dtype,
+                             cudaStream_t stream) {
+  if (n_requests <= 0) return 0;
+  if (taps < 1 || taps > MAX_TAPS) MI_REFUSE("rglru: %d taps (1 to %d are taken)", taps, MAX_TAPS);
+  if (bw <= 0 || C % bw) MI_REFUSE("rglru: %d channels are no whole number of blocks of %d", C, bw);
+  if (n_requests > 65535) MI_REFUSE("rglru: too many requests for one launch");
+  const int threads = C >= 2048 ? 64 : 32;   // many small blocks: the walk is latency-bound
+  dim3 grid((C + threads - 1) / threads, n_requests);
+  if (dtype == MI_DTYPE_F32)
+    MI_LAUNCH((rglru_scan_kernel<float>), grid, threads, 0, stream, gates, M, bw, br, bi, lam, decay_scale,
+              (const float*)u, u_stride, (const float*)y, y_stride, y_bias, (const float*)xin, xin_stride, xin_bias,
+              state, state_stride, taps, q_start, q_len, state_slot, (float*)out, out_stride, C);
+  else if (dtype == MI_DTYPE_BF16)
+    MI_LAUNCH((rglru_scan_kernel<bf16>), grid, threads, 0, stream, gates, M, bw, br, bi, lam, decay_scale,
+              (const bf16*)u, u_stride, (const bf16*)y, y_stride, y_bias, (const bf16*)xin, xin_stride, xin_bias,
+              state, state_stride, taps, q_start, q_len, state_slot, (bf16*)out, out_stride, C);
+  else
+    MI_REFUSE("rglru: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------------------------------
+// gated linear attention.  A block owns 32 value columns of one head of one request; thread
+// (tx, ty) keeps rows ty*R .. ty*R+R-1 of column tx of the state in registers.  Tokens are taken in
+// groups of GL: q, k, alpha and v of a group are staged in shared memory, every thread walks the
+// group updating its rows and leaving its share of each o in shared memory, and the shares are
+// added in a fixed order.
+// ------------------------------------------------------------------------------------------
+#define GLA_R 8
+#define GLA_L 16
+
+template <typename T>
+__global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int stride,
+                                const float* __restrict__ z, int z_stride, const float* __restrict__ z_bias,
+                                float inv_tau, float q_scale, float* __restrict__ state, long long state_stride,
+                                const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                const int* __restrict__ state_slot, float* __restrict__ o, int o_stride,
+                                int heads, int dk, int dv) {
+  mi_pdl_enter();
+  extern __shared__ float sm[];
+  const int KP = blockDim.y;
+  float* qs = sm;                       // [GLA_L][dk]
+  float* ks = qs + GLA_L * dk;          // [GLA_L][dk]
+  float* as = ks + GLA_L * dk;          // [GLA_L][dk]
+  float* vs = as + GLA_L * dk;          // [GLA_L][32]
+  float* part = vs + GLA_L * 32;        // [GLA_L][KP][32]
+  const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * 32 + tx, nthreads = KP * 32;
+  const int head = blockIdx.y, req = blockIdx.z;
+  const int j = blockIdx.x * 32 + tx;   // value column
+  const int len = q_len[req], row0 = q_start[req];
+  float* S = state + (size_t)state_slot[req] * state_stride + (size_t)head * dk * dv;
+  float s[GLA_R];
+#pragma unroll
+  for (int i = 0; i < GLA_R; ++i) {
+    const int kk = ty * GLA_R + i;
+    s[i] = (kk < dk && j < dv) ? S[(size_t)kk * dv + j] : 0.f;
+  }
+  for (int t0 = 0; t0 < len; t0 += GLA_L) {
+    const int n = min(GLA_L, len - t0);
+    __syncthreads();   // the group before is consumed
+    for (int idx = tid; idx < n * dk; idx += nthreads) {
+      const int l = idx / dk, kk = idx - l * dk;
+      const size_t m = (size_t)(row0 + t0 + l);
+      qs[l * dk + kk] = mi_to_float(q[m * stride + head * dk + kk]) * q_scale;
+      ks[l * dk + kk] = mi_to_float(k[m * stride + head * dk + kk]);
+      const float zz = z[m * z_stride + head * dk + kk] + (z_bias ? z_bias[head * dk + kk] : 0.f);
+      // sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau)
+      as[l * dk + kk] = expf(-mi_softplus(-zz) * inv_tau);
+    }
+    for (int idx = tid; idx < n * 32; idx += nthreads) {
+      const int l = idx >> 5, jj = blockIdx.x * 32 + (idx & 31);
+      vs[idx] = jj < dv ? mi_to_float(v[(size_t)(row0 + t0 + l) * stride + head * dv + jj]) : 0.f;
+    }
+    __syncthreads();
+    for (int l = 0; l < n; ++l) {
+      const float vv = vs[l * 32 + tx];
+      float po = 0.f;
+#pragma unroll
+      for (int i = 0; i < GLA_R; ++i) {
+        const int kk = ty * GLA_R + i;
+        if (kk < dk) {
+          s[i] = fmaf(as[l * dk + kk], s[i], ks[l * dk + kk] * vv);
+          po = fmaf(s[i], qs[l * dk + kk], po);
+        }
+      }
+      part[(l * KP + ty) * 32 + tx] = po;
+    }
+    __syncthreads();
+    for (int l = ty; l < n; l += KP) {
+      float sum = 0.f;
+      for (int p = 0; p < KP; ++p) sum += part[(l * KP + p) * 32 + tx];
+      if (j < dv) o[(size_t)(row0 + t0 + l) * o_stride + head * dv + j] = sum;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < GLA_R; ++i) {
+    const int kk = ty * GLA_R + i;
+    if (kk < dk && j < dv) S[(size_t)kk * dv + j] = s[i];
+  }
+}
+
+extern "C" int mi_gla_scan(const void* q, const void* k, const void* v, int stride, const float* z, int z_stride,
+                           const float* z_bias, float inv_tau, float q_scale, float* state, long long state_stride,
+                           const int* q_start, const int* q_len, const int* state_slot, float* o, int o_stride,
+                           int n_requests, int heads, int dk, int dv, int dtype, cudaStream_t stream) {
+  if (n_requests <= 0) return 0;
+  if (dk <= 0 || dk > 256 || dv <= 0) MI_REFUSE("gla: key size %d must lie in [1, 256], value size %d above 0", dk, dv);
+  if (heads > 65535 || n_requests > 65535) MI_REFUSE("gla: too many heads or requests for one launch");
+  const int KP = (dk + GLA_R - 1) / GLA_R;
+  dim3 grid((dv + 31) / 32, heads, n_requests), block(32, KP);
+  const size_t smem = ((size_t)3 * GLA_L * dk + GLA_L * 32 + (size_t)GLA_L * KP * 32) * sizeof(float);
+#define MI_GO(T)                                                                                          \
+  do {                                                                                                    \
+    auto kern = gla_scan_kernel<T>;                                                                       \
+    if (smem > 48 * 1024) {                                                                               \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                                \
+    }                                                                                                     \
+    MI_LAUNCH(kern, grid, block, smem, stream, (const T*)q, (const T*)k, (const T*)v, stride, z, z_stride,  \
+              z_bias, inv_tau, q_scale, state, state_stride, q_start, q_len, state_slot, o, o_stride, heads, dk, dv); \
+  } while (0)
+  if (dtype == MI_DTYPE_F32) MI_GO(float);
+  else if (dtype == MI_DTYPE_BF16) MI_GO(bf16);
+  else MI_REFUSE("gla: unknown dtype %d", dtype);
+#undef MI_GO
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------------------------------
+// per-head RMS norm with a shared gain, times an activated gate.  One warp per (token, head).
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void headnorm_gate_kernel(const float* __restrict__ o, int o_stride, const float* __restrict__ w,
+                                     const T* __restrict__ g, int g_stride, T* __restrict__ out, int out_stride,
+                                     int M, int heads, int dv, float eps, int act, float scale) {
+  mi_pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= (long long)M * heads) return;
+  const int t = (int)(unit / heads), h = (int)(unit - (long long)t * heads);
+  const float* src = o + (size_t)t * o_stride + h * dv;
+  float ss = 0.f;
+  for (int c = lane; c < dv; c += 32) ss += src[c] * src[c];
+  ss = mi_warp_sum(ss);
+  const float mult = 1.f / sqrtf(ss / (float)dv + eps);
+  for (int c = lane; c < dv; c += 32) {
+    float a = 1.f;
+    if (act) {
+      const float gv = mi_to_float(g[(size_t)t * g_stride + h * dv + c]);
+      const float sg = 1.f / (1.f + expf(-gv));
+      a = act == 2 ? gv * sg : sg;
+    }
+    out[(size_t)t * out_stride + h * dv + c] = mi_from_float<T>(src[c] * mult * w[c] * a * scale);
+  }
+}
+
+extern "C" int mi_headnorm_gate(const float* o, int o_stride, const float* w, const void* g, int g_stride,
+                                void* out, int out_stride, int M, int heads, int dv, float eps, int act,
+                                float scale, int dtype, cudaStream_t stream) {
+  if (M <= 0 || heads <= 0) return 0;
+  if (act < 0 || act > 2) MI_REFUSE("headnorm_gate: unknown activation %d", act);
+  const long long units = (long long)M * heads;
+  const long long blocks = (units + 3) / 4;
+  if (blocks > 0x7fffffffLL) MI_REFUSE("headnorm_gate: too many blocks for one launch");
+  if (dtype == MI_DTYPE_F32)
+    MI_LAUNCH((headnorm_gate_kernel<float>), (unsigned)blocks, 128, 0, stream, o, o_stride, w, (const float*)g,
+              g_stride, (float*)out, out_stride, M, heads, dv, eps, act, scale);
+  else if (dtype == MI_DTYPE_BF16)
+    MI_LAUNCH((headnorm_gate_kernel<bf16>), (unsigned)blocks, 128, 0, stream, o, o_stride, w, (const bf16*)g,
+              g_stride, (bf16*)out, out_stride, M, heads, dv, eps, act, scale);
+  else
+    MI_REFUSE("headnorm_gate: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}

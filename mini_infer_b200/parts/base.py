@@ -39,20 +39,25 @@ class ParamDecl:
     ``matrix``  operand of a matrix product; converted to the compute dtype when bound
     ``gain``    multiplicative vector of a norm; a 32-bit stored gain stays 32-bit
     ``table``   anything else (kept as loaded)
+
+    A size of ``None`` in ``shape`` is given by the checkpoint (the part reads it from the tensor it
+    is bound to); random weights need every size.
     """
 
-    shape: tuple[int, ...]
+    shape: tuple[int | None, ...]
     role: str = "matrix"
 
 
 @dataclass(frozen=True)
 class KVNeed:
     """Per-token keys and values kept in pages: ``kv_heads * head_dim`` numbers each per
-    token.  ``window``: only the last ``window`` positions are ever read (None: all)."""
+    token.  ``window``: only the last ``window`` positions are ever read (None: all).
+    ``value_dim``: size of a value per head where it is not ``head_dim`` (keys keep ``head_dim``)."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None
 
 
 @dataclass(frozen=True)
@@ -247,6 +252,19 @@ class DeferredNorm:
         return self.x.shape
 
 
+class BranchSum(tuple):
+    """Outputs of several branches that read the same stream and whose sum is still to be added to
+    it: what a layer with parallel branches hands on in the place of a single ``x``.  A norm that
+    knows it adds the parts to the fp32 stream one by one (no rounded sum in between); any other
+    part may ask for ``total()``."""
+
+    def total(self) -> torch.Tensor:
+        out = self[0]
+        for t in self[1:]:
+            out = out + t
+        return out
+
+
 class Norm(Part):
     # What kind of unfinished norm this class can leave to the products around it (``"rms"``: the
     # product before adds to the stream, multiplies by the gain and leaves sums of squares; the
@@ -390,7 +408,7 @@ def register_head(kind: str, cls, *, replace: bool = False) -> None:
 
 
 def lookup(family: str, kind: str):
-    from . import builtin  # noqa: F401  (registers the parts that ship with the package)
+    from . import builtin, experts, mixers  # noqa: F401  (register the parts that ship with the package)
 
     try:
         return _REGISTRIES[family][kind]

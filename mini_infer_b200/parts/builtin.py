@@ -14,6 +14,7 @@ import torch
 from ..csrc import ops
 from .base import (
     Arrangement,
+    BranchSum,
     DeferredNorm,
     FeedForward,
     KVNeed,
@@ -106,12 +107,62 @@ class RMSNorm(Norm):
             if x.norm is not self or rows is not None:
                 raise ValueError("a deferred norm was handed to another norm than the one it was made for")
             return x, x.residual
+        if isinstance(x, BranchSum):
+            x = x.total()
         if rows is not None:
             return ops.add_rmsnorm(x, self.weight, self.eps, residual_in=residual, rows=rows), None
         new_residual = torch.empty(x.shape, dtype=torch.float32, device=x.device)
         out = ops.add_rmsnorm(x, self.weight, self.eps, residual_in=residual,
                               residual_out=new_residual)
         return out, new_residual
+
+
+class LayerNorm(Norm):
+    """``(r - mean(r)) / sqrt(var(r) + eps) * w + b`` with ``r = x + residual`` in fp32, the variance
+    being the mean of the squared deviations.  ``x`` may be a ``BranchSum``: its parts are added to
+    the stream one by one in fp32.  The stream is updated in place.
+
+    params: ``hidden_size``, ``eps``.  tensors: ``weight [hidden_size]``, ``bias [hidden_size]``.
+    """
+
+    def param_decls(self):
+        H = int(self.param("hidden_size"))
+        return {"weight": ParamDecl((H,), "gain"), "bias": ParamDecl((H,), "table")}
+
+    def bind(self, tensors, dtype, device):
+        self.weight = tensors["weight"].to(torch.float32).contiguous()
+        self.bias = tensors["bias"].to(torch.float32).contiguous()
+        self.eps = float(self.param("eps"))
+        self.dtype = dtype
+
+    @staticmethod
+    def stream_and_addends(x, residual):
+        """The fp32 stream and what is still to be added to it, from a layer's ``(x, residual)``:
+        before the first layer ``x`` is the embedding and becomes the stream."""
+        if residual is None:
+            if isinstance(x, BranchSum):
+                x = x.total()
+            return (x if x.dtype == torch.float32 else x.to(torch.float32)).contiguous(), ()
+        return residual, (tuple(x) if isinstance(x, BranchSum) else (x,))
+
+    def forward(self, x, residual, rows=None):
+        stream, adds = self.stream_and_addends(x, residual)
+        out, = ops.add_layernorm(stream, adds, [(self.weight, self.bias)], self.eps, self.dtype, rows=rows)
+        return out, (None if rows is not None else stream)
+
+    def forward_with(self, other: "LayerNorm", x, residual):
+        """This norm and ``other`` of the same stream in one pass: ``(out_self, out_other, stream)``."""
+        stream, adds = self.stream_and_addends(x, residual)
+        a, b = ops.add_layernorm(stream, adds, [(self.weight, self.bias), (other.weight, other.bias)],
+                                 self.eps, self.dtype)
+        return a, b, stream
+
+
+class NoNorm(Norm):
+    """The place of a norm in a layer that has nothing behind it (a layer without a feed-forward)."""
+
+    def forward(self, x, residual, rows=None):
+        raise RuntimeError("a layer asked the norm of a branch it does not have")
 
 
 # ----------------------------------------------------------------------------- position
@@ -186,6 +237,31 @@ class RotaryPosition(Position):
                            slots=ctx.groups[cache.group].slots, kcache=cache.k, vcache=cache.v)
         else:
             self.encode(qkv, nq, nkv, head_dim, ctx)
+
+
+class InterleavedRotary(Position):
+    """Rotary encoding, interleaved layout: on the first ``rotary_dim`` dimensions of a head,
+    dimension ``2i`` pairs with ``2i + 1`` and the pair ``(u, v)`` at position ``p`` becomes
+    ``(u cos a - v sin a, v cos a + u sin a)``, ``a = p * theta^(-2i / rotary_dim)``; the other
+    dimensions pass.  The frequencies are rounded once from float64; angles, sines and cosines are
+    fp32 in the kernel.  A mixer with a fused kernel reads ``inv_freq`` and ``rotary_dim`` itself.
+
+    params: ``head_dim``, ``theta``, optional ``rotary_dim`` (default ``head_dim``).
+    """
+
+    def bind(self, tensors, dtype, device):
+        d = int(self.param("head_dim"))
+        self.rotary_dim = int(self.spec.params.get("rotary_dim") or d)
+        if self.rotary_dim % 2 or not 0 < self.rotary_dim <= d:
+            raise ValueError(f"{self.rotary_dim} rotated dimensions of a head of {d}")
+        theta = float(self.param("theta"))
+        i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+        self.inv_freq = (theta ** (-2.0 * i / self.rotary_dim)).to(torch.float32).to(device)
+
+    def encode(self, qkv, nq, nkv, head_dim, ctx):
+        ops.rope_norm_store(qkv, 0, nq * head_dim, (nq + nkv) * head_dim, nq, nkv, head_dim, head_dim,
+                            positions=ctx.positions, inv_freq=self.inv_freq, rot=self.rotary_dim,
+                            unit_norm=False, eps=0.0)
 
 
 # ----------------------------------------------------------------------------- mixer
@@ -316,9 +392,10 @@ class SwiGLU(FeedForward):
 
 
 class TokenEmbedding(Part):
-    """``h0 = E[token]``, no scale (reference ``models/llama/llama.py:104,159``).
+    """``h0 = E[token]`` (reference ``models/llama/llama.py:104,159``), or with ``scale``
+    ``h0 = float(E[token]) * scale``, which is then the fp32 residual stream itself.
 
-    params: ``vocab_size``, ``hidden_size``.  tensors: ``weight [vocab, hidden]``.
+    params: ``vocab_size``, ``hidden_size``, optional ``scale``.  tensors: ``weight [vocab, hidden]``.
     """
 
     def param_decls(self):
@@ -328,6 +405,9 @@ class TokenEmbedding(Part):
         self.weight = _as_compute(tensors["weight"], dtype).contiguous()
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
+        scale = self.spec.params.get("scale")
+        if scale is not None:
+            return ops.embedding_scaled(self.weight, ctx.token_ids, float(scale))
         return ops.embedding(self.weight, ctx.token_ids)
 
 
@@ -402,7 +482,43 @@ class PreNormBlock(Arrangement):
         return f, residual
 
 
+class ParallelBlock(Arrangement):
+    """``h += mixer(norm1(h)) + ffn(norm2(h))``: both branches read the same stream.  The block
+    receives the previous layer's branch outputs (a ``BranchSum``, or the embedding before the first
+    layer) with the fp32 stream that does not yet include them, adds them while it normalises, and
+    returns its own branch outputs unadded.  Two ``LayerNorm``s of one ``eps`` run as one kernel.
+    A layer without a feed-forward (``no_feed_forward``) has the mixer's branch alone."""
+
+    def forward(self, x, residual, ctx, cache):
+        ff = None if isinstance(self.feed_forward, NoFeedForward) else self.feed_forward
+        n1, n2 = self.mixer_norm, self.feed_forward_norm
+        if ff is None:
+            a, stream = n1.forward(x, residual)
+            return self.mixer.forward(a, ctx, cache, self.position), stream
+        if isinstance(n1, LayerNorm) and isinstance(n2, LayerNorm) and n1.eps == n2.eps:
+            a, b, stream = n1.forward_with(n2, x, residual)
+        else:
+            a, stream = n1.forward(x, residual)
+            zero = torch.zeros_like(a)          # any pair of norms: the second one sees the same stream
+            b, _ = n2.forward(zero, stream.clone())
+        m = self.mixer.forward(a, ctx, cache, self.position)
+        f = ff.forward(b, ctx)
+        return BranchSum((m, f)), stream
+
+
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward."""
+
+    def forward(self, x, ctx):
+        raise RuntimeError("this layer has no feed-forward")
+
+
 register_norm("rmsnorm", RMSNorm, replace=True)
+register_norm("layernorm", LayerNorm, replace=True)
+register_norm("no_norm", NoNorm, replace=True)
+register_position("rotary_interleaved", InterleavedRotary, replace=True)
+register_feed_forward("no_feed_forward", NoFeedForward, replace=True)
+register_arrangement("parallel", ParallelBlock, replace=True)
 register_position("rotary", RotaryPosition, replace=True)
 register_mixer("gqa_attention", GroupedQueryAttention, replace=True)
 register_feed_forward("swiglu", SwiGLU, replace=True)

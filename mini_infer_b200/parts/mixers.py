@@ -1,0 +1,331 @@
+"""Mixers beyond plain grouped-query attention: a sliding-window attention with unit-norm queries
+and keys and gated heads, two recurrent mixers that keep a state of fixed size per request (the
+real-gated linear recurrent unit and gated linear attention), and a mixer that runs two of them
+side by side on the same input.
+
+They share one shape (``ProjectedMixer``): everything a mixer projects from its input is one
+stacked matrix, everything it hands to its output projection is one row of activations.  A mixer
+alone runs ``input product -> mix -> output product``; side by side, the input matrices of both
+are stacked into one product and the output matrices into another, and each mixer only fills its
+columns.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import KVNeed, LayerCache, Mixer, ParamDecl, PlanNeeds, StateNeed, StepContext, build_part, register_mixer
+from .builtin import InterleavedRotary, Linear, _as_compute
+from .spec import PartSpec
+
+
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.float32).contiguous()
+
+
+class ProjectedMixer(Mixer):
+    """A mixer as ``W_out mix(W_in h)``.  Subclasses give ``in_width``/``out_width``, build
+    ``self.w_in [in_width, H]`` and ``self.w_out [H, out_width]`` in ``bind``, and implement
+    ``mix(proj, out, out_scale, ctx, cache, position)``, which reads the projected row ``proj
+    [M, in_width]`` (a column range; it may be overwritten) and writes ``out [M, out_width]``
+    (a column range) times ``out_scale``."""
+
+    in_width: int
+    out_width: int
+    w_in: torch.Tensor
+    w_out: torch.Tensor
+
+    def mix(self, proj: torch.Tensor, out: torch.Tensor, out_scale: float, ctx: StepContext, cache: LayerCache,
+            position) -> None:
+        raise NotImplementedError
+
+    def finish_bind(self) -> None:
+        self._in, self._out = Linear(self.w_in), Linear(self.w_out)
+
+    def forward(self, x, ctx, cache, position):
+        proj = self._in(x)
+        out = torch.empty((ctx.n_tokens, self.out_width), dtype=x.dtype, device=x.device)
+        self.mix(proj, out, 1.0, ctx, cache, position)
+        return self._out(out)
+
+
+# ----------------------------------------------------------------------------- windowed attention
+
+
+class GatedWindowAttention(ProjectedMixer):
+    """Softmax attention over a sliding window (position ``i`` sees ``j`` with ``0 <= i - j <
+    window``; no window: all of the past) with ``num_heads`` query heads sharing ``num_kv_heads``
+    key/value heads, keys of ``head_dim`` and values of ``value_dim`` per head.  After the position
+    encoding (an ``InterleavedRotary``, or none) queries and keys are divided by their root mean
+    square over the head (``qk_unit_norm``); the score is ``q . k * scale``; the heads' outputs are
+    multiplied by ``sigmoid(W_g h)`` (``gate``) before the output projection.  Scores, weights and
+    sums are fp32 for either dtype.
+
+    params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``; optional ``value_dim``
+    (default ``head_dim``), ``window``, ``scale`` (default ``head_dim ** -0.5``), ``qk_unit_norm``
+    (default False) with ``eps``, ``gate`` (None or ``"sigmoid"`` / ``"silu"``).
+    tensors: ``q``, ``k``, ``v``, ``o`` and, with a gate, ``g``.
+    """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        g = self.spec.params.get
+        self.hidden = int(self.param("hidden_size"))
+        self.nq, self.nkv = int(self.param("num_heads")), int(self.param("num_kv_heads"))
+        self.d = int(self.param("head_dim"))
+        self.dv = int(g("value_dim") or self.d)
+        self.window = int(g("window")) if g("window") else None
+        self.scale = float(g("scale")) if g("scale") is not None else self.d ** -0.5
+        self.unit_norm = bool(g("qk_unit_norm", False))
+        self.eps = float(g("eps", 0.0))
+        self.gate = g("gate")
+        if self.nq % self.nkv:
+            raise ValueError(f"{self.nq} query heads cannot share {self.nkv} key/value heads")
+        if not (0 < self.d <= 256 and 0 < self.dv <= 256):
+            raise ValueError(f"head sizes {self.d} and {self.dv} must lie in [1, 256]")
+        if self.gate not in (None, "sigmoid", "silu"):
+            raise ValueError(f"unknown gate {self.gate!r}")
+        self.q_off = 0
+        self.k_off = self.nq * self.d
+        self.v_off = self.k_off + self.nkv * self.d
+        self.g_off = self.v_off + self.nkv * self.dv
+        self.in_width = self.g_off + (self.nq * self.dv if self.gate else 0)
+        self.out_width = self.nq * self.dv
+
+    def param_decls(self):
+        H, nq, nkv, d, dv = self.hidden, self.nq, self.nkv, self.d, self.dv
+        decls = {"q": ParamDecl((nq * d, H)), "k": ParamDecl((nkv * d, H)), "v": ParamDecl((nkv * dv, H)),
+                 "o": ParamDecl((H, nq * dv))}
+        if self.gate:
+            decls["g"] = ParamDecl((nq * dv, H))
+        return decls
+
+    def cache_need(self):
+        return KVNeed(self.nkv, self.d, self.window, None if self.dv == self.d else self.dv)
+
+    def plan_needs(self):
+        return PlanNeeds(frozenset({ops.ATTENTION_TILE_TOKENS}))
+
+    def bind(self, tensors, dtype, device):
+        names = ["q", "k", "v"] + (["g"] if self.gate else [])
+        self.w_in = torch.cat([_as_compute(tensors[n], dtype) for n in names], dim=0).contiguous()
+        self.w_out = _as_compute(tensors["o"], dtype).contiguous()
+        self.finish_bind()
+
+    def mix(self, proj, out, out_scale, ctx, cache, position):
+        nq, nkv, d, dv = self.nq, self.nkv, self.d, self.dv
+        if position is not None and not isinstance(position, InterleavedRotary):
+            raise ValueError("this attention takes an interleaved rotary encoding or none")
+        group = ctx.groups[cache.group]
+        ops.rope_norm_store(
+            proj, self.q_off, self.k_off, self.v_off, nq, nkv, d, dv,
+            positions=ctx.positions if position is not None else None,
+            inv_freq=position.inv_freq if position is not None else None,
+            rot=position.rotary_dim if position is not None else 0,
+            unit_norm=self.unit_norm, eps=self.eps,
+            slots=group.slots if cache.writes else None,
+            kcache=cache.k if cache.writes else None, vcache=cache.v if cache.writes else None)
+        q = proj[:, self.q_off:self.q_off + nq * d]
+        if self.gate:
+            heads = torch.empty((ctx.n_tokens, nq * dv), dtype=proj.dtype, device=proj.device)
+            ops.attention_kv(q, heads, cache, ctx, nq, nkv, d, dv, self.scale, self.window or 0)
+            ops.gate_mul(heads, proj[:, self.g_off:self.g_off + nq * dv], out, self.gate, out_scale)
+        elif out_scale == 1.0:
+            ops.attention_kv(q, out, cache, ctx, nq, nkv, d, dv, self.scale, self.window or 0)
+        else:
+            raise ValueError("an ungated attention cannot scale its output")
+
+
+# ----------------------------------------------------------------------------- gated linear attention
+
+
+class GatedLinearAttention(ProjectedMixer):
+    """Per head a matrix state ``S [key_dim, value_dim]`` in fp32, carried from token to token:
+    ``S_t = diag(alpha_t) S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t`` with ``q = W_q h * key_dim^-0.5``
+    and a decay per key channel ``alpha = sigmoid(W_a2 (W_a1 h) + b)^(1 / tau)``.  Each head's ``o``
+    gets an RMS norm over ``value_dim`` with one gain shared by the heads; the heads are multiplied by
+    ``silu(W_g h)`` and projected.
+
+    params: ``hidden_size``, ``num_heads``, ``key_dim``, ``value_dim``, ``tau``, ``eps``, ``decay_rank``
+    (None: the rank is the one the checkpoint's ``a1`` has).
+    tensors: ``q``, ``k``, ``v``, ``g``, ``o``, ``norm``, ``a1``, ``a2``, ``a2.b``.
+    """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.param("hidden_size"))
+        self.heads = int(self.param("num_heads"))
+        self.dk, self.dv = int(self.param("key_dim")), int(self.param("value_dim"))
+        self.tau = float(self.param("tau"))
+        rank = self.spec.params.get("decay_rank")
+        self.rank = int(rank) if rank else None
+        self.eps = float(self.param("eps"))
+        if not 0 < self.dk <= 256:
+            raise ValueError(f"key size {self.dk} must lie in [1, 256]")
+        hk, hv = self.heads * self.dk, self.heads * self.dv
+        self.q_off, self.k_off, self.v_off = 0, hk, 2 * hk
+        self.g_off = 2 * hk + hv
+        self.a_off = self.g_off + hv
+        self.out_width = hv
+
+    @property
+    def in_width(self) -> int:
+        return self.a_off + self.rank
+
+    def param_decls(self):
+        H, hk, hv = self.hidden, self.heads * self.dk, self.heads * self.dv
+        return {"q": ParamDecl((hk, H)), "k": ParamDecl((hk, H)), "v": ParamDecl((hv, H)), "g": ParamDecl((hv, H)),
+                "o": ParamDecl((H, hv)), "norm": ParamDecl((self.dv,), "gain"),
+                "a1": ParamDecl((self.rank, H)), "a2": ParamDecl((hk, self.rank)), "a2.b": ParamDecl((hk,), "table")}
+
+    def state_need(self):
+        return StateNeed((self.heads, self.dk, self.dv), torch.float32)
+
+    def bind(self, tensors, dtype, device):
+        self.rank = int(tensors["a1"].shape[0])
+        self.w_in = torch.cat([_as_compute(tensors[n], dtype) for n in ("q", "k", "v", "g", "a1")], dim=0).contiguous()
+        self.w_out = _as_compute(tensors["o"], dtype).contiguous()
+        self.a2 = Linear(_as_compute(tensors["a2"], dtype).contiguous())
+        self.a2_bias = _f32(tensors["a2.b"])
+        self.norm_gain = _f32(tensors["norm"])
+        self.finish_bind()
+
+    def mix(self, proj, out, out_scale, ctx, cache, position):
+        hk, hv = self.heads * self.dk, self.heads * self.dv
+        low = proj[:, self.a_off:self.a_off + self.rank]
+        z = self.a2(low if low.data_ptr() % 16 == 0 else low.contiguous(), out_dtype=torch.float32)
+        o = ops.gla_scan(proj[:, self.q_off:self.q_off + hk], proj[:, self.k_off:self.k_off + hk],
+                         proj[:, self.v_off:self.v_off + hv], z, self.a2_bias, self.tau, self.dk ** -0.5,
+                         self.heads, self.dk, self.dv, cache.state, ctx)
+        ops.headnorm_gate(o, self.norm_gain, proj[:, self.g_off:self.g_off + hv], out, self.heads, self.dv,
+                          self.eps, "silu", out_scale)
+
+
+# ----------------------------------------------------------------------------- real-gated linear recurrent unit
+
+
+class RealGatedLinearRecurrence(ProjectedMixer):
+    """Two branches of ``width`` channels: ``y = gelu_tanh(W_y h + b_y)`` and ``u = conv(W_x h + b_x)``,
+    a causal convolution per channel over ``conv_taps`` tokens (the last tap meets the current
+    token).  ``u`` is cut into ``blocks`` parts; in each, ``r = sigmoid(A_r u + b_r)`` and ``i =
+    sigmoid(A_i u + b_i)`` with square matrices.  Then ``a = exp(-decay_scale * r * softplus(lam))``
+    and ``S_t = a S_(t-1) + sqrt(1 - a^2) * i * u`` from ``S = 0``; the output is ``W_o (S * y)``.
+    The state (fp32, per request) is ``S`` and the convolution's last ``conv_taps - 1`` inputs.
+
+    params: ``hidden_size``, ``width``, ``blocks``, ``conv_taps``, optional ``decay_scale`` (default 8).
+    tensors: ``y``, ``y.b``, ``x``, ``x.b``, ``conv``, ``conv.b``, ``ra``, ``ra.b``, ``ri``, ``ri.b``, ``lam``, ``o``.
+    """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.param("hidden_size"))
+        self.width = int(self.param("width"))
+        self.blocks = int(self.param("blocks"))
+        self.taps = int(self.param("conv_taps"))
+        self.decay_scale = float(self.spec.params.get("decay_scale", 8.0))
+        if self.blocks <= 0 or self.width % self.blocks:
+            raise ValueError(f"{self.width} channels cannot be cut into {self.blocks} equal parts")
+        if not 1 <= self.taps <= 16:
+            raise ValueError(f"{self.taps} convolution taps (1 to 16 are taken)")
+        self.in_width = 2 * self.width
+        self.out_width = self.width
+
+    def param_decls(self):
+        H, C, B = self.hidden, self.width, self.blocks
+        bw = C // B
+        return {"y": ParamDecl((C, H)), "y.b": ParamDecl((C,), "table"), "x": ParamDecl((C, H)),
+                "x.b": ParamDecl((C,), "table"), "conv": ParamDecl((C, self.taps), "table"),
+                "conv.b": ParamDecl((C,), "table"), "ra": ParamDecl((B, bw, bw)), "ra.b": ParamDecl((B, bw), "table"),
+                "ri": ParamDecl((B, bw, bw)), "ri.b": ParamDecl((B, bw), "table"), "lam": ParamDecl((C,), "table"),
+                "o": ParamDecl((H, C))}
+
+    def state_need(self):
+        return StateNeed((self.taps, self.width), torch.float32)
+
+    def bind(self, tensors, dtype, device):
+        self.w_in = torch.cat([_as_compute(tensors["y"], dtype), _as_compute(tensors["x"], dtype)], dim=0).contiguous()
+        self.w_out = _as_compute(tensors["o"], dtype).contiguous()
+        self.y_bias, self.x_bias = _f32(tensors["y.b"]), _f32(tensors["x.b"])
+        self.conv_w, self.conv_b = _f32(tensors["conv"]), _f32(tensors["conv.b"])
+        self.gates_w = torch.cat([_as_compute(tensors["ra"], dtype), _as_compute(tensors["ri"], dtype)],
+                                 dim=1).contiguous()                       # [blocks, 2 bw, bw]
+        self.gate_bias_r, self.gate_bias_i = _f32(tensors["ra.b"]).reshape(-1), _f32(tensors["ri.b"]).reshape(-1)
+        self.lam = _f32(tensors["lam"])
+        self.finish_bind()
+
+    def mix(self, proj, out, out_scale, ctx, cache, position):
+        if out_scale != 1.0:
+            raise ValueError("this mixer cannot scale its output")
+        C = self.width
+        y, x = proj[:, :C], proj[:, C:2 * C]
+        u = torch.empty((ctx.n_tokens, C), dtype=proj.dtype, device=proj.device)
+        ops.causal_conv(x, self.x_bias, self.conv_w, self.conv_b, cache.state, ctx, u)
+        gates = ops.block_diagonal_gates(u, self.gates_w)
+        ops.rglru_scan(gates, self.gate_bias_r, self.gate_bias_i, self.lam, self.decay_scale, u, y, self.y_bias,
+                       x, self.x_bias, self.taps, cache.state, ctx, out)
+
+
+# ----------------------------------------------------------------------------- two mixers side by side
+
+
+class SideBySide(Mixer):
+    """Two mixers that read the same input: ``left_scale * left(h) + right_scale * right(h)``.  Both
+    are ``ProjectedMixer``s, so their input matrices are stacked into one product and their output
+    matrices, side by side, into another; the scales ride on what each writes for that product.  At
+    most one of them keeps keys and values and at most one a state (a layer's cache holds one of each).
+
+    params: ``left``, ``right`` (each a ``PartSpec`` of a registered mixer, its ``prefix`` relative to
+    this part's), ``left_scale``, ``right_scale``.
+    """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.children: list[ProjectedMixer] = []
+        self.scales: list[float] = []
+        for side in ("left", "right"):
+            child: PartSpec = self.param(side)
+            part = build_part("mixer", PartSpec(child.kind, child.params, prefix=child.prefix, rename=child.rename))
+            if not isinstance(part, ProjectedMixer):
+                raise ValueError(f"mixer {child.kind!r} cannot run side by side with another")
+            self.children.append(part)
+            self.scales.append(float(self.spec.params.get(side + "_scale", 1.0)))
+        if sum(c.cache_need() is not None for c in self.children) > 1 or \
+                sum(c.state_need() is not None for c in self.children) > 1:
+            raise ValueError("side by side, at most one mixer may keep keys and values and one a state")
+
+    def param_decls(self):
+        return {c.spec.prefix + local: decl for c in self.children for local, decl in c.param_decls().items()}
+
+    def cache_need(self):
+        return next((n for n in (c.cache_need() for c in self.children) if n is not None), None)
+
+    def state_need(self):
+        return next((n for n in (c.state_need() for c in self.children) if n is not None), None)
+
+    def plan_needs(self):
+        return PlanNeeds(frozenset().union(*(c.plan_needs().q_tile_tokens for c in self.children)))
+
+    def bind(self, tensors, dtype, device):
+        for c in self.children:
+            c.bind({local: tensors[c.spec.prefix + local] for local in c.param_decls()}, dtype, device)
+        self._in = Linear(torch.cat([c.w_in for c in self.children], dim=0).contiguous())
+        self._out = Linear(torch.cat([c.w_out for c in self.children], dim=1).contiguous())
+        for c in self.children:      # the stacked copies are the ones that run
+            c.w_in = c.w_out = c._in = c._out = None
+
+    def forward(self, x, ctx, cache, position):
+        proj = self._in(x)
+        out = torch.empty((ctx.n_tokens, sum(c.out_width for c in self.children)), dtype=x.dtype, device=x.device)
+        i0 = o0 = 0
+        for c, scale in zip(self.children, self.scales):
+            c.mix(proj[:, i0:i0 + c.in_width], out[:, o0:o0 + c.out_width], scale, ctx, cache, position)
+            i0 += c.in_width
+            o0 += c.out_width
+        return self._out(out)
+
+
+register_mixer("gated_window_attention", GatedWindowAttention, replace=True)
+register_mixer("gated_linear_attention", GatedLinearAttention, replace=True)
+register_mixer("rglru", RealGatedLinearRecurrence, replace=True)
+register_mixer("side_by_side", SideBySide, replace=True)

@@ -164,6 +164,6 @@ class DecoderModel:
             after = self.blocks[self.schedule[i + 1].layer].entry() if i + 1 < len(self.schedule) else None
             x, residual = block.forward(x, residual, ctx, cache, following=after)
         if n_want == 0:
-            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
         z, _ = self.final_norm.forward(x, residual, rows=want_rows)
         return self.head.forward(z)

@@ -50,10 +50,13 @@ def check_names(model, names_and_shapes: dict[str, tuple[int, ...]], where: str 
     ignorable = model.ignorable_tensors()
     missing = sorted(n for n in expected if n not in names_and_shapes)
     unexpected = sorted(n for n in names_and_shapes if n not in expected and n not in ignorable)
+    def fits(want, found) -> bool:      # a declared size of None is whatever the checkpoint has
+        return len(want) == len(found) and all(w is None or w == f for w, f in zip(want, found))
+
     mismatched = sorted(
         (n, tuple(expected[n]), tuple(names_and_shapes[n]))
         for n in expected
-        if n in names_and_shapes and tuple(names_and_shapes[n]) != tuple(expected[n])
+        if n in names_and_shapes and not fits(tuple(expected[n]), tuple(names_and_shapes[n]))
     )
     if missing or unexpected or mismatched:
         lines = [f"weights in {where} do not fit the model:"]

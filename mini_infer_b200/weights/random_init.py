@@ -149,6 +149,9 @@ def random_tensor(seed: int, name: str, shape, role: str, *, std: float, gain_st
     ``1 + N(0, gain_std)`` for a norm's gain; the same values on every device.  Computed in
     float64, rounded once to float32 and then to ``dtype``."""
     key = tensor_seed(seed, name)
+    if any(n is None for n in shape):
+        raise ValueError(f"tensor {name!r} has a size that only a checkpoint gives ({tuple(shape)}); "
+                         "random weights need it in the configuration")
     shape = tuple(int(n) for n in shape)
     total = 1
     for n in shape:
