@@ -25,7 +25,7 @@ rope_norm_store_kernel(T* __restrict__ qkv, int stride, int q_off, int k_off, in
   mi_pdl_enter();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const float pos = (float)positions[t];
+  const float pos = positions ? (float)positions[t] : 0.f;
   T* row = qkv + (size_t)t * stride;
   constexpr int EPC = 16 / (int)sizeof(T);
   const int slot = writes ? slots[t] : 0;

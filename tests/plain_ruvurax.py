@@ -166,11 +166,15 @@ def clamped_expert(h: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: 
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ down.T
 
 
-def moe(h: torch.Tensor, W: dict, mlp: dict) -> torch.Tensor:
+def moe(h: torch.Tensor, W: dict, mlp: dict, margins: list | None = None) -> torch.Tensor:
     """Every token: the ``top`` experts with the largest router logits, weighted by the softmax
-    over those logits alone, plus a shared expert."""
+    over those logits alone, plus a shared expert.  ``margins`` collects, per token, how far the
+    last chosen logit lies above the first one left out (a test must not rest on a close call)."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     z = h @ W["router"].T
+    if margins is not None and top < E:
+        ordered = torch.sort(z, dim=-1, descending=True).values
+        margins.append(ordered[:, top - 1] - ordered[:, top])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         vals, idx = torch.topk(z[t], top)
@@ -186,7 +190,8 @@ def moe(h: torch.Tensor, W: dict, mlp: dict) -> torch.Tensor:
 # ------------------------------------------------------------------------------- the model
 
 
-def ruvurax_forward(state: dict, cfg: dict, tokens, dtype=torch.float64, return_layers: bool = False):
+def ruvurax_forward(state: dict, cfg: dict, tokens, dtype=torch.float64, return_layers: bool = False,
+                    margins: list | None = None):
     """Logits ``[T, vocab]`` of one sequence from position 0 (and, on request, the residual stream
     after every layer)."""
     W = {k: v.to(dtype) for k, v in state.items()}
@@ -206,7 +211,7 @@ def ruvurax_forward(state: dict, cfg: dict, tokens, dtype=torch.float64, return_
             raise ValueError(layer["type"])
         if layer.get("mlp"):
             b = layer_norm(x, W[p + "norm2"], W[p + "norm2.b"], eps)
-            mix = mix + moe(b, sub(W, p + "mlp."), layer["mlp"])
+            mix = mix + moe(b, sub(W, p + "mlp."), layer["mlp"], margins)
         x = x + mix
         streams.append(x)
     logits = layer_norm(x, W["final.norm"], W["final.norm.b"], eps) @ W["head"].T
