@@ -105,7 +105,23 @@ class GatedWindowAttention(ProjectedMixer):
         return KVNeed(self.nkv, self.d, self.window, None if self.dv == self.d else self.dv)
 
     def plan_needs(self):
-        return PlanNeeds(frozenset({ops.ATTENTION_TILE_TOKENS}))
+        tiles = {ops.ATTENTION_TILE_TOKENS}
+        if self._tensor_core_sizes():
+            tiles |= set(ops.attention_tile_sizes(self.nq // self.nkv))
+        return PlanNeeds(frozenset(tiles))
+
+    def _tensor_core_sizes(self) -> bool:
+        """Sizes the tensor-core attention kernels take: keys and values of one size, a multiple of 16."""
+        return self.d == self.dv and self.d % 16 == 0 and 16 <= self.d <= 256
+
+    def _attend(self, q, heads, cache, ctx):
+        """bfloat16 with sizes the tensor-core kernels take and aligned rows: those kernels (scores and
+        softmax in fp32, as everywhere); else the CUDA-core kernel."""
+        if (q.dtype == torch.bfloat16 and self._tensor_core_sizes() and heads.is_contiguous()
+                and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
+            ops.attention(q, q.stride(0), heads, cache, ctx, self.nq, self.nkv, self.d, self.scale, self.window or 0)
+        else:
+            ops.attention_kv(q, heads, cache, ctx, self.nq, self.nkv, self.d, self.dv, self.scale, self.window or 0)
 
     def bind(self, tensors, dtype, device):
         names = ["q", "k", "v"] + (["g"] if self.gate else [])
@@ -129,10 +145,10 @@ class GatedWindowAttention(ProjectedMixer):
         q = proj[:, self.q_off:self.q_off + nq * d]
         if self.gate:
             heads = torch.empty((ctx.n_tokens, nq * dv), dtype=proj.dtype, device=proj.device)
-            ops.attention_kv(q, heads, cache, ctx, nq, nkv, d, dv, self.scale, self.window or 0)
+            self._attend(q, heads, cache, ctx)
             ops.gate_mul(heads, proj[:, self.g_off:self.g_off + nq * dv], out, self.gate, out_scale)
         elif out_scale == 1.0:
-            ops.attention_kv(q, out, cache, ctx, nq, nkv, d, dv, self.scale, self.window or 0)
+            self._attend(q, out, cache, ctx)
         else:
             raise ValueError("an ungated attention cannot scale its output")
 
