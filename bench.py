@@ -271,6 +271,107 @@ def time_e2e(runner, batch: int, context: int, steps: int, warmup: int) -> dict:
             "h2d_bytes_per_step": runner.stepper.last_h2d_bytes, "d2h_bytes_per_step": 4 * batch}
 
 
+# ---------------------------------------------------------------------------------------------
+# ``--scenario designs``: the Ruvurax architecture beside Llama at equal width, heads, layer count
+# and per-token feed-forward size (random weights), prefill and decode.  A line of its own.
+# ---------------------------------------------------------------------------------------------
+
+DESIGN_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, rot=64, r_heads=4, r_dim=128, r_vdim=256,
+               rank=16, unit_width=2560, blocks=10, conv=4, experts=32, top=4, ff=512, shared_ff=1024, vocab=32000),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, rot=128, r_heads=8, r_dim=128, r_vdim=256,
+               rank=16, unit_width=4096, blocks=16, conv=4, experts=64, top=4, ff=1024, shared_ff=2048, vocab=32000),
+}
+
+
+def design_configs(s: dict, layers: int) -> tuple[dict, dict]:
+    """(Ruvurax configuration, Llama configuration of the same width, heads and per-token feed-forward)."""
+    mlp = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"]},
+           "expert": {"ff": s["ff"], "limit": 7.0}, "shared": {"ff": s["shared_ff"], "limit": 7.0}}
+    unit = {"type": "rglru", "mixer": {"width": s["unit_width"], "blocks": s["blocks"], "conv": s["conv"]}, "mlp": mlp}
+    both = {"type": "parallel", "mlp": mlp,
+            "mixer": {"left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                               "mask": {"size": s["window"]}, "rot": {"base": 10000.0, "dims": s["rot"]},
+                               "scale": s["dim"] ** -0.5},
+                      "right": {"heads": s["r_heads"], "dim": s["r_dim"], "vdim": s["r_vdim"], "tau": 16.0,
+                                "rank": s["rank"]},
+                      "left_scale": 1.0, "right_scale": 1.0}}
+    ruvurax = {"architecture": "Ruvurax", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0},
+               "norm": {"eps": 1e-6}, "layers": [unit if i % 2 == 0 else both for i in range(layers)]}
+    llama = dict(LLAMA_8B, hidden_size=s["width"], num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"],
+                 head_dim=s["dim"], intermediate_size=s["top"] * s["ff"] + s["shared_ff"], vocab_size=s["vocab"],
+                 num_hidden_layers=layers)
+    return ruvurax, llama
+
+
+def design_matmul_params(s: dict, layers: int, batch_tokens: int | None) -> float:
+    """Matrix elements a step of the Ruvurax configuration reads (``batch_tokens``: a decode step, which
+    touches only the experts its tokens chose, in expectation) or multiplies a token with (None)."""
+    H, E, top = s["width"], s["experts"], s["top"]
+    hit = E * (1.0 - (1.0 - 1.0 / E) ** (batch_tokens * top)) if batch_tokens else top
+    mlp = H * E + hit * 3 * H * s["ff"] + 3 * H * s["shared_ff"]
+    C, bw = s["unit_width"], s["unit_width"] // s["blocks"]
+    unit = 3 * H * C + 2 * C * bw
+    d, hk, hv = s["dim"], s["r_heads"] * s["r_dim"], s["r_heads"] * s["r_vdim"]
+    left = H * d * (3 * s["heads"] + 2 * s["kv_heads"])              # q, g, o and k, v
+    right = H * (2 * hk + 3 * hv) + H * s["rank"] + s["rank"] * hk
+    n_unit = (layers + 1) // 2
+    return n_unit * (unit + mlp) + (layers - n_unit) * (left + right + mlp) + s["vocab"] * H
+
+
+def run_designs(args) -> int:
+    import torch
+
+    from mini_infer_b200.engine import ModelRunner
+
+    peaks = load_peaks()
+    warmup = max(3, args.warmup)
+    out = {"scenario": "designs", "dtype": "bf16", "data": "synthetic", "batch": args.batch, "context": args.context,
+           "prefill_tokens": PREFILL_TOKENS, "peaks": peaks, "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name in args.design_sizes.split(","):
+        s = DESIGN_SIZES[name]
+        layers = args.layers or 4
+        ruvurax, llama = design_configs(s, layers)
+        cap = args.batch * (args.context + args.steps + warmup + 64) + 2 * PREFILL_TOKENS
+        row = {"layers": layers}
+        for label, raw in (("ruvurax", ruvurax), ("llama", llama)):
+            runner = ModelRunner.from_random(raw, seed=0, gain_std=0.0, device="cuda:0", dtype="bfloat16",
+                                             num_blocks=cap // PAGE + 8, block_size=PAGE, max_requests=args.batch,
+                                             cuda_graph=True)
+            ms, launches = time_decode(runner, args.batch, args.context, args.steps, warmup)
+            pms = time_prefill(runner, PREFILL_TOKENS, repeats=3, warmup=2)
+            if label == "llama":
+                flops = prefill_flops(raw, layers, PREFILL_TOKENS)
+                nbytes = decode_bytes(raw, layers, args.batch, args.context + warmup + args.steps / 2.0)
+            else:
+                n_both = layers // 2
+                window = min(s["window"], PREFILL_TOKENS)
+                attention = n_both * 4.0 * PREFILL_TOKENS * window * s["heads"] * s["dim"]   # an upper bound
+                linear = n_both * 4.0 * PREFILL_TOKENS * s["r_heads"] * s["r_dim"] * s["r_vdim"]
+                flops = 2.0 * PREFILL_TOKENS * (design_matmul_params(s, layers, None) - s["vocab"] * s["width"]) \
+                    + 2.0 * s["vocab"] * s["width"] + attention + linear
+                cache = 2.0 * args.batch * min(s["window"], args.context) * 2 * s["kv_heads"] * s["dim"] * n_both
+                state = 8.0 * args.batch * (n_both * s["r_heads"] * s["r_dim"] * s["r_vdim"]
+                                            + (layers - n_both) * s["conv"] * s["unit_width"])
+                nbytes = 2.0 * design_matmul_params(s, layers, args.batch) + cache + state
+            row[label] = {
+                "decode_tok_s": round(args.batch * 1000.0 / ms, 1), "decode_ms": round(ms, 4),
+                "decode_gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
+                "decode_frac_of_hbm": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pms, 1), "prefill_ms": round(pms, 3),
+                "prefill_frac_of_bf16": round(flops / (pms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+                "launches_per_decode_step": launches // max(1, args.steps),
+            }
+            del runner
+            torch.cuda.empty_cache()
+        out["sizes"][name] = row
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def run_long_mixed(args) -> int:
     """The long mixed workload: ``--requests`` requests started together, prompt lengths drawn
     log-uniformly from [16, ``--max-prompt``], ``--generate`` greedy tokens each, a step budget
@@ -697,10 +798,13 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when decoding starts")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 and e2e measurements")
-    ap.add_argument("--scenario", default="decode", choices=["decode", "long-mixed", "serving"],
+    ap.add_argument("--scenario", default="decode", choices=["decode", "long-mixed", "serving", "designs"],
                     help="decode: the contract line; long-mixed: many requests of very different lengths "
                          "through the scheduler (a line of its own); serving: the reference's published "
-                         "workload, 1024 tokens in and 128 out, single requests and 16 together (a line of its own)")
+                         "workload, 1024 tokens in and 128 out, single requests and 16 together (a line of its own); "
+                         "designs: the Ruvurax architecture beside Llama at equal sizes, prefill and decode "
+                         "(a line of its own)")
+    ap.add_argument("--design-sizes", default="2k,4k", help="designs: which of the sizes " + ",".join(DESIGN_SIZES))
     ap.add_argument("--requests", type=int, default=64, help="long-mixed: requests started together")
     ap.add_argument("--max-prompt", type=int, default=32768, help="long-mixed: longest prompt")
     ap.add_argument("--generate", type=int, default=256, help="long-mixed: tokens generated per request")
@@ -726,6 +830,9 @@ def main() -> int:
         return reference_arm(args)
     if args.scenario == "long-mixed":
         return run_long_mixed(args)
+    if args.scenario == "designs":
+        args.layers = None if args.layers == default_layers else args.layers
+        return run_designs(args)
     warmup = max(3, args.warmup)
 
     import torch

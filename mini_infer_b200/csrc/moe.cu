@@ -1,7 +1,8 @@
 // Routed experts: every token goes through the `top` experts its router picks.
 //
-//   mi_moe_route      z = W_r x in fp32; the `top` largest logits of a token (ties: the lower index) and
-//                     the softmax over those alone -> ids [M, top] int32, weights [M, top] fp32
+//   mi_moe_select     from the router logits z = W_r x (fp32, a matrix product): the `top` largest of a token
+//                     (ties: the lower index) and the softmax over those alone -> ids [M, top] int32,
+//                     weights [M, top] fp32
 //   mi_moe_plan       sorts the M*top (token, choice) entries by expert: perm[pos] = entry, inv[entry] =
 //                     pos, offsets[E + 1], and the list of row tiles (expert, first row, rows) that the
 //                     grouped products walk.  Nothing comes back to the host: the products are launched
@@ -13,8 +14,9 @@
 //
 // glu(g, u) = g' * sigmoid(alpha * g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit).
 //
-// The products run on CUDA cores with fp32 accumulation, k ascending, so a row's result does not
-// depend on which other rows share its tile.
+// float32 products run on CUDA cores with fp32 accumulation, k ascending; bfloat16 products run on the
+// tensor cores (mma.sync m16n8k16, fp32 accumulation, k ascending).  Either way a row's result does
+// not depend on which other rows share its tile.
 #include "common.cuh"
 
 MI_DEFINE_ERROR_API()
@@ -26,27 +28,22 @@ __device__ __forceinline__ float mi_clamped_glu_value(float g, float u, float li
 }
 
 // ------------------------------------------------------------------------------------------ router
+// The logits [M, E] (fp32) come from a matrix product; one warp per token picks the `top` largest
+// (ties: the lower index) and takes the softmax over those alone.
 #define ROUTE_MAX_PER_LANE 8
 
-template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ wr,
-                                 int* __restrict__ ids, float* __restrict__ weights, int M, int H, int E, int top) {
+__global__ void moe_select_kernel(const float* __restrict__ logits, int stride, int* __restrict__ ids,
+                                  float* __restrict__ weights, int M, int E, int top) {
   mi_pdl_enter();
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= M) return;
-  const T* xr = x + (size_t)t * x_stride;
+  const float* z = logits + (size_t)t * stride;
   float lg[ROUTE_MAX_PER_LANE];
 #pragma unroll
-  for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) lg[i] = -INFINITY;
-  for (int e = 0; e < E; ++e) {
-    const T* w = wr + (size_t)e * H;
-    float acc = 0.f;
-    for (int h = lane; h < H; h += 32) acc = fmaf(mi_to_float(xr[h]), mi_to_float(w[h]), acc);
-    acc = mi_warp_sum(acc);
-#pragma unroll
-    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
-      if (e == lane + 32 * i) lg[i] = acc;
+  for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    lg[i] = e < E ? z[e] : -INFINITY;
   }
   float my_val = 0.f, denom = 0.f, first = 0.f;
   int my_id = 0;
@@ -87,20 +84,12 @@ __global__ void moe_route_kernel(const T* __restrict__ x, int x_stride, const T*
   }
 }
 
-extern "C" int mi_moe_route(const void* x, int x_stride, const void* wr, int* ids, float* weights, int M, int H,
-                            int E, int top, int dtype, cudaStream_t stream) {
+extern "C" int mi_moe_select(const float* logits, int stride, int* ids, float* weights, int M, int E, int top,
+                             cudaStream_t stream) {
   if (M <= 0) return 0;
   if (E <= 0 || E > 32 * ROUTE_MAX_PER_LANE) MI_REFUSE("moe: %d experts (1 to %d are taken)", E, 32 * ROUTE_MAX_PER_LANE);
   if (top <= 0 || top > E || top > 32) MI_REFUSE("moe: %d of %d experts per token", top, E);
-  const int blocks = (M + 3) / 4;
-  if (dtype == MI_DTYPE_F32)
-    MI_LAUNCH((moe_route_kernel<float>), blocks, 128, 0, stream, (const float*)x, x_stride, (const float*)wr, ids,
-              weights, M, H, E, top);
-  else if (dtype == MI_DTYPE_BF16)
-    MI_LAUNCH((moe_route_kernel<bf16>), blocks, 128, 0, stream, (const bf16*)x, x_stride, (const bf16*)wr, ids,
-              weights, M, H, E, top);
-  else
-    MI_REFUSE("moe: unknown dtype %d", dtype);
+  MI_LAUNCH((moe_select_kernel), (M + 3) / 4, 128, 0, stream, logits, stride, ids, weights, M, E, top);
   MI_RETURN_LAUNCH_STATUS();
 }
 
@@ -241,6 +230,138 @@ moe_gemm_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w0,
   }
 }
 
+// ------------------------------------------------------------------------------------------ the same on tensor cores
+// bfloat16 only.  64 rows x 64 columns per block, k in steps of 32; four warps, each 32 x 32 of the
+// tile as 2 x 4 mma.m16n8k16 tiles (twice that with two weight matrices).  Operands go through
+// shared memory with rows of 40 elements, which makes the fragments' 32-bit reads conflict-free.
+// Rows of 8 elements are fetched as one 16-byte load where k and the pointers allow it.
+#define MMA_K 32
+#define MMA_LD (MMA_K + 8)
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// 64 rows x 32 k of a row-major operand into shared memory; row pointers may be null (zero rows)
+__device__ __forceinline__ void mma_stage(bf16 (*dst)[MMA_LD], const bf16* const* rowptr, int k0, int K, bool vec,
+                                          int tid) {
+  if (vec) {   // 64 rows x 4 chunks of 8 elements: 2 chunks per thread
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int idx = tid + 128 * it;
+      const int r = idx >> 2, c8 = (idx & 3) << 3;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      const bf16* src = rowptr[r];
+      if (src && k0 + c8 < K) v = *reinterpret_cast<const uint4*>(src + k0 + c8);   // K % 8 == 0: whole chunks
+      *reinterpret_cast<uint4*>(&dst[r][c8]) = v;
+    }
+  } else {
+    for (int idx = tid; idx < TILE_M * MMA_K; idx += 128) {
+      const int r = idx / MMA_K, kk = idx - r * MMA_K;
+      const bf16* src = rowptr[r];
+      dst[r][kk] = (src && k0 + kk < K) ? src[k0 + kk] : __float2bfloat16_rn(0.f);
+    }
+  }
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restrict__ w0, const bf16* __restrict__ w1,
+                    long long w_expert_stride, const int* __restrict__ perm, int top, const int* __restrict__ plan,
+                    int E, void* __restrict__ out_, int N, int K, float limit, float alpha, int vec) {
+  mi_pdl_enter();
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int* td = plan + 2 + E + 3 * tile;
+  const int e = td[0], row0 = td[1], rows = td[2];
+  const int n0 = blockIdx.x * TILE_N;
+  __shared__ __align__(16) bf16 As[TILE_M][MMA_LD];
+  __shared__ __align__(16) bf16 B0[TILE_N][MMA_LD];
+  __shared__ __align__(16) bf16 B1[GATED ? TILE_N : 1][MMA_LD];
+  __shared__ const bf16* aptr[TILE_M];
+  __shared__ const bf16* b0ptr[TILE_N];
+  __shared__ const bf16* b1ptr[TILE_N];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp >> 1, wn = warp & 1, g = lane >> 2, t = lane & 3;
+  const bf16* wb0 = w0 + (size_t)e * w_expert_stride;
+  const bf16* wb1 = GATED ? w1 + (size_t)e * w_expert_stride : nullptr;
+  if (tid < TILE_M) {
+    const bf16* p = nullptr;
+    if (tid < rows) p = a + (size_t)(GATED ? perm[row0 + tid] / top : row0 + tid) * a_stride;
+    aptr[tid] = p;
+    const int n = n0 + tid;
+    b0ptr[tid] = n < N ? wb0 + (size_t)n * K : nullptr;
+    b1ptr[tid] = (GATED && n < N) ? wb1 + (size_t)n * K : nullptr;
+  }
+  float acc0[2][4][4], acc1[GATED ? 2 : 1][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        acc0[i][j][c] = 0.f;
+        if (GATED) acc1[i][j][c] = 0.f;
+      }
+  __syncthreads();
+  for (int k0 = 0; k0 < K; k0 += MMA_K) {
+    mma_stage(As, aptr, k0, K, vec != 0, tid);
+    mma_stage(B0, b0ptr, k0, K, vec != 0, tid);
+    if (GATED) mma_stage(B1, b1ptr, k0, K, vec != 0, tid);
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < MMA_K; ks += 16) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = wm * 32 + i * 16 + g;
+        af[i][0] = *reinterpret_cast<const uint32_t*>(&As[r][ks + 2 * t]);
+        af[i][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][ks + 2 * t]);
+        af[i][2] = *reinterpret_cast<const uint32_t*>(&As[r][ks + 2 * t + 8]);
+        af[i][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][ks + 2 * t + 8]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = wn * 32 + j * 8 + g;
+        uint32_t bf[2];
+        bf[0] = *reinterpret_cast<const uint32_t*>(&B0[n][ks + 2 * t]);
+        bf[1] = *reinterpret_cast<const uint32_t*>(&B0[n][ks + 2 * t + 8]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) mma_bf16(acc0[i][j], af[i], bf);
+        if (GATED) {
+          bf[0] = *reinterpret_cast<const uint32_t*>(&B1[n][ks + 2 * t]);
+          bf[1] = *reinterpret_cast<const uint32_t*>(&B1[n][ks + 2 * t + 8]);
+#pragma unroll
+          for (int i = 0; i < 2; ++i) mma_bf16(acc1[i][j], af[i], bf);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int r = wm * 32 + i * 16 + g + (c >> 1) * 8;
+        const int n = n0 + wn * 32 + j * 8 + 2 * t + (c & 1);
+        if (r >= rows || n >= N) continue;
+        if (GATED)
+          reinterpret_cast<bf16*>(out_)[(size_t)(row0 + r) * N + n] =
+              __float2bfloat16_rn(mi_clamped_glu_value(acc0[i][j][c], acc1[i][j][c], limit, alpha));
+        else
+          reinterpret_cast<float*>(out_)[(size_t)(row0 + r) * N + n] = acc0[i][j][c];
+      }
+}
+
+// whether rows of k elements starting at these pointers can be fetched in 16-byte pieces
+static int mma_vec_ok(const void* a, long long a_stride, const void* w0, const void* w1, int K) {
+  return K % 8 == 0 && a_stride % 8 == 0 && mi_aligned(a, 16) && mi_aligned(w0, 16) && (!w1 || mi_aligned(w1, 16));
+}
+
 static int max_tiles(int n_entries, int E) { return (n_entries + TILE_M - 1) / TILE_M + E; }
 
 extern "C" int mi_moe_gate_up(const void* x, int x_stride, const void* w_gate, const void* w_up,
@@ -254,8 +375,9 @@ extern "C" int mi_moe_gate_up(const void* x, int x_stride, const void* w_gate, c
     MI_LAUNCH((moe_gemm_kernel<float, true>), grid, 256, 0, stream, (const float*)x, x_stride, (const float*)w_gate,
               (const float*)w_up, w_expert_stride, perm, top, plan, E, act, ff, H, limit, alpha);
   else if (dtype == MI_DTYPE_BF16)
-    MI_LAUNCH((moe_gemm_kernel<bf16, true>), grid, 256, 0, stream, (const bf16*)x, x_stride, (const bf16*)w_gate,
-              (const bf16*)w_up, w_expert_stride, perm, top, plan, E, act, ff, H, limit, alpha);
+    MI_LAUNCH((moe_gemm_mma_kernel<true>), grid, 128, 0, stream, (const bf16*)x, x_stride, (const bf16*)w_gate,
+              (const bf16*)w_up, w_expert_stride, perm, top, plan, E, act, ff, H, limit, alpha,
+              mma_vec_ok(x, x_stride, w_gate, w_up, H));
   else
     MI_REFUSE("moe: unknown dtype %d", dtype);
   MI_RETURN_LAUNCH_STATUS();
@@ -270,8 +392,9 @@ extern "C" int mi_moe_down(const void* act, const void* w_down, long long w_expe
     MI_LAUNCH((moe_gemm_kernel<float, false>), grid, 256, 0, stream, (const float*)act, ff, (const float*)w_down,
               (const float*)nullptr, w_expert_stride, (const int*)nullptr, 1, plan, E, (void*)y, H, ff, 0.f, 0.f);
   else if (dtype == MI_DTYPE_BF16)
-    MI_LAUNCH((moe_gemm_kernel<bf16, false>), grid, 256, 0, stream, (const bf16*)act, ff, (const bf16*)w_down,
-              (const bf16*)nullptr, w_expert_stride, (const int*)nullptr, 1, plan, E, (void*)y, H, ff, 0.f, 0.f);
+    MI_LAUNCH((moe_gemm_mma_kernel<false>), grid, 128, 0, stream, (const bf16*)act, ff, (const bf16*)w_down,
+              (const bf16*)nullptr, w_expert_stride, (const int*)nullptr, 1, plan, E, (void*)y, H, ff, 0.f, 0.f,
+              mma_vec_ok(act, ff, w_down, nullptr, ff));
   else
     MI_REFUSE("moe: unknown dtype %d", dtype);
   MI_RETURN_LAUNCH_STATUS();

@@ -225,6 +225,12 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
     lib.mi_rglru_scan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int,
                                   c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, ll, c_int,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    lib.mi_rglru_scan_chunked.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int,
+                                          c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, ll, c_int,
+                                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
+                                          c_int, c_int, c_void_p]
+    lib.mi_rglru_chunked_scratch.argtypes = [c_int, c_int, c_int]
+    lib.mi_rglru_chunked_scratch.restype = ll
     lib.mi_gla_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
                                 c_void_p, ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_int, c_int, c_void_p]
@@ -234,8 +240,7 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
 
 def _sig_moe(lib: ctypes.CDLL) -> None:
     ll = ctypes.c_longlong
-    lib.mi_moe_route.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                 c_void_p]
+    lib.mi_moe_select.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     lib.mi_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.mi_moe_tile_rows.restype = c_int
     lib.mi_moe_gate_up.argtypes = [c_void_p, c_int, c_void_p, c_void_p, ll, c_void_p, c_int, c_void_p, c_int,
@@ -1237,6 +1242,9 @@ def _max_q_len(ctx) -> int:
     return 1 if ctx.decode_only else max(ctx.host_q_len)
 
 
+RGLRU_CHUNK = 64     # tokens per chunk of the chunked walk; portions up to this long are walked plainly
+
+
 def rglru_scan(gates: torch.Tensor, gate_bias_r: torch.Tensor, gate_bias_i: torch.Tensor, lam: torch.Tensor,
                decay_scale: float, u: torch.Tensor, y: torch.Tensor, y_bias: torch.Tensor | None,
                x_in: torch.Tensor, x_in_bias: torch.Tensor | None, taps: int, state: torch.Tensor, ctx,
@@ -1263,6 +1271,23 @@ def rglru_scan(gates: torch.Tensor, gate_bias_r: torch.Tensor, gate_bias_i: torc
     if stride < taps * C:
         raise KernelError("rglru: state row too short")
     lib = _lib("recurrent")
+    longest = _max_q_len(ctx)
+    if u.dtype == torch.bfloat16 and longest > RGLRU_CHUNK:
+        # long portions: chunks side by side (the float32 path keeps the plain walk, whose sums do not
+        # depend on where a portion starts)
+        global launch_count
+        n_chunks = -(-longest // RGLRU_CHUNK)
+        scratch = torch.empty(lib.mi_rglru_chunked_scratch(ctx.n_requests, n_chunks, C), dtype=torch.float32,
+                              device=u.device)
+        rc = lib.mi_rglru_scan_chunked(_ptr(gates), M, bw, _ptr(gate_bias_r), _ptr(gate_bias_i), _ptr(lam),
+                                       float(decay_scale), _ptr(u), u.stride(0), _ptr(y), y.stride(0), _ptr(y_bias),
+                                       _ptr(x_in), x_in.stride(0), _ptr(x_in_bias), _ptr(state), stride, int(taps),
+                                       _ptr(ctx.q_start), _ptr(ctx.q_len), _ptr(ctx.state_slot), _ptr(out),
+                                       out.stride(0), ctx.n_requests, C, _ptr(scratch), n_chunks, RGLRU_CHUNK,
+                                       _code(u.dtype), _stream())
+        _finish(lib, rc, "rglru")
+        launch_count += 1
+        return
     rc = lib.mi_rglru_scan(_ptr(gates), M, bw, _ptr(gate_bias_r), _ptr(gate_bias_i), _ptr(lam), float(decay_scale),
                            _ptr(u), u.stride(0), _ptr(y), y.stride(0), _ptr(y_bias), _ptr(x_in), x_in.stride(0),
                            _ptr(x_in_bias), _ptr(state), stride, int(taps), _ptr(ctx.q_start), _ptr(ctx.q_len),
@@ -1333,12 +1358,12 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, top: int) -> tuple[torch.Te
         raise KernelError("moe: the router must be a contiguous [experts, H] matrix in x's dtype")
     M, H = x.shape
     E = router.shape[0]
+    logits = linear(x, router, out_dtype=torch.float32)      # exact products, fp32 sums, for either dtype
     ids = torch.empty((M, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((M, top), dtype=torch.float32, device=x.device)
     lib = _lib("moe")
-    rc = lib.mi_moe_route(_ptr(x), x.stride(0), _ptr(router), _ptr(ids), _ptr(weights), M, H, E, int(top),
-                          _code(x.dtype), _stream())
-    _finish(lib, rc, "moe_route")
+    rc = lib.mi_moe_select(_ptr(logits), logits.stride(0), _ptr(ids), _ptr(weights), M, E, int(top), _stream())
+    _finish(lib, rc, "moe_select")
     return ids, weights
 
 

@@ -3,7 +3,8 @@
 // Every request of a step brings q_len[b] consecutive tokens (rows q_start[b] .. of the packed
 // activations) and owns row state_slot[b] of a state arena (fp32, zeroed when the request is
 // admitted).  All recurrences run in fp32, token by token in the order of the positions, so a
-// result never depends on how a prompt was cut into steps or on what else is in the batch.
+// result never depends on how a prompt was cut into steps or on what else is in the batch (the
+// chunked walk of long bfloat16 portions folds whole chunks first, which moves the fp32 rounding).
 //
 //   mi_causal_conv     per channel: out[t] = b + sum_j w[j] * in[t - (taps-1-j)], in = x + x_bias,
 //                      with the taps-1 inputs before the portion taken from the state (zeros before
@@ -165,6 +166,125 @@ extern "C" int mi_rglru_scan(const float* gates, int M, int bw, const float* br,
               state, state_stride, taps, q_start, q_len, state_slot, (bf16*)out, out_stride, C);
   else
     MI_REFUSE("rglru: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------------------------------
+// The same recurrence for long portions, cut into chunks of `chunk` tokens that run side by side.
+// Pass 1: every (request, chunk, channel) folds its chunk into S_end = A * S_begin + B.  Pass 2: it
+// walks the chunks before its own to get S_begin (from the state as pass 1 saved it), then its own
+// tokens exactly as the walk above does.  The last chunk stores the state and the convolution's tail.
+// scratch: [requests][max_chunks][2][C] chunk summaries, then [requests][C] the states at the start.
+// ------------------------------------------------------------------------------------------
+struct RglruTerms { float a, b; };
+
+template <typename T>
+__device__ __forceinline__ RglruTerms rglru_terms(const float* g, int bw, float vbr, float vbi, float sp, const T* u,
+                                                  size_t row, int u_stride, int c) {
+  const float r = mi_sigmoid(g[0] + vbr), ig = mi_sigmoid(g[bw] + vbi);
+  const float log_a = -sp * r;
+  RglruTerms t;
+  t.a = expf(log_a);
+  t.b = sqrtf(-expm1f(2.f * log_a)) * (ig * mi_to_float(u[row * u_stride + c]));
+  return t;
+}
+
+template <typename T, int PASS>
+__global__ void rglru_chunk_kernel(const float* __restrict__ gates, int M, int bw,
+                                   const float* __restrict__ br, const float* __restrict__ bi,
+                                   const float* __restrict__ lam, float decay_scale,
+                                   const T* __restrict__ u, int u_stride,
+                                   const T* __restrict__ y, int y_stride, const float* __restrict__ y_bias,
+                                   const T* __restrict__ xin, int xin_stride, const float* __restrict__ xin_bias,
+                                   float* __restrict__ state, long long state_stride, int taps,
+                                   const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                   const int* __restrict__ state_slot, T* __restrict__ out, int out_stride, int C,
+                                   float* __restrict__ scratch, int max_chunks, int chunk, int n_requests) {
+  mi_pdl_enter();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int ci = blockIdx.y, req = blockIdx.z;
+  if (c >= C) return;
+  const int len = q_len[req], row0 = q_start[req];
+  const int t0 = ci * chunk;
+  if (t0 >= len) return;
+  const int t1 = min(len, t0 + chunk);
+  float* st = state + (size_t)state_slot[req] * state_stride;
+  float* summ = scratch + ((size_t)req * max_chunks) * 2 * C;
+  float* start = scratch + (size_t)n_requests * max_chunks * 2 * C + (size_t)req * C;
+  const int blk = c / bw, cj = c - blk * bw;
+  const float* g = gates + ((size_t)blk * M + row0 + t0) * (2 * bw) + cj;
+  const float vbr = br[c], vbi = bi[c];
+  const float sp = decay_scale * mi_softplus(lam[c]);
+  if (PASS == 1) {
+    float A = 1.f, B = 0.f;
+    for (int t = t0; t < t1; ++t, g += 2 * bw) {
+      const RglruTerms k = rglru_terms(g, bw, vbr, vbi, sp, u, (size_t)(row0 + t), u_stride, c);
+      B = fmaf(k.a, B, k.b);
+      A *= k.a;
+    }
+    summ[((size_t)ci * 2) * C + c] = A;
+    summ[((size_t)ci * 2 + 1) * C + c] = B;
+    if (ci == 0) start[c] = st[(size_t)(taps - 1) * C + c];
+    return;
+  }
+  float S = start[c];
+  for (int p = 0; p < ci; ++p) S = fmaf(summ[((size_t)p * 2) * C + c], S, summ[((size_t)p * 2 + 1) * C + c]);
+  const float yb = y_bias ? y_bias[c] : 0.f;
+  for (int t = t0; t < t1; ++t, g += 2 * bw) {
+    const RglruTerms k = rglru_terms(g, bw, vbr, vbi, sp, u, (size_t)(row0 + t), u_stride, c);
+    S = fmaf(k.a, S, k.b);
+    const float yv = mi_gelu_tanh(mi_to_float(y[(size_t)(row0 + t) * y_stride + c]) + yb);
+    out[(size_t)(row0 + t) * out_stride + c] = mi_from_float<T>(S * yv);
+  }
+  if (t1 < len) return;
+  st[(size_t)(taps - 1) * C + c] = S;
+  if (taps > 1) {
+    const float xb = xin_bias ? xin_bias[c] : 0.f;
+    float keep[MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j) {
+      if (j < taps - 1) {
+        const int src = len - (taps - 1) + j;
+        keep[j] = src >= 0 ? mi_to_float(xin[(size_t)(row0 + src) * xin_stride + c]) + xb
+                           : st[(size_t)(taps - 1 + src) * C + c];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j)
+      if (j < taps - 1) st[(size_t)j * C + c] = keep[j];
+  }
+}
+
+extern "C" long long mi_rglru_chunked_scratch(int n_requests, int max_chunks, int C) {
+  return ((long long)n_requests * max_chunks * 2 + n_requests) * C;
+}
+
+extern "C" int mi_rglru_scan_chunked(const float* gates, int M, int bw, const float* br, const float* bi,
+                                     const float* lam, float decay_scale, const void* u, int u_stride, const void* y,
+                                     int y_stride, const float* y_bias, const void* xin, int xin_stride,
+                                     const float* xin_bias, float* state, long long state_stride, int taps,
+                                     const int* q_start, const int* q_len, const int* state_slot, void* out,
+                                     int out_stride, int n_requests, int C, float* scratch, int max_chunks, int chunk,
+                                     int dtype, cudaStream_t stream) {
+  if (n_requests <= 0 || max_chunks <= 0) return 0;
+  if (taps < 1 || taps > MAX_TAPS) MI_REFUSE("rglru: %d taps (1 to %d are taken)", taps, MAX_TAPS);
+  if (bw <= 0 || C % bw) MI_REFUSE("rglru: %d channels are no whole number of blocks of %d", C, bw);
+  if (chunk <= 0 || max_chunks > 65535 || n_requests > 65535) MI_REFUSE("rglru: too many chunks or requests for one launch");
+  dim3 grid((C + 127) / 128, max_chunks, n_requests);
+#define MI_GO(T, PASS)                                                                                               \
+  MI_LAUNCH((rglru_chunk_kernel<T, PASS>), grid, 128, 0, stream, gates, M, bw, br, bi, lam, decay_scale, (const T*)u, \
+            u_stride, (const T*)y, y_stride, y_bias, (const T*)xin, xin_stride, xin_bias, state, state_stride, taps,   \
+            q_start, q_len, state_slot, (T*)out, out_stride, C, scratch, max_chunks, chunk, n_requests)
+  if (dtype == MI_DTYPE_F32) {
+    MI_GO(float, 1);
+    MI_GO(float, 2);
+  } else if (dtype == MI_DTYPE_BF16) {
+    MI_GO(bf16, 1);
+    MI_GO(bf16, 2);
+  } else {
+    MI_REFUSE("rglru: unknown dtype %d", dtype);
+  }
+#undef MI_GO
   MI_RETURN_LAUNCH_STATUS();
 }
 

@@ -246,13 +246,18 @@ def test_interleaved_rotation_unit_norm_and_store(d, dv, rot):
     assert torch.equal(got[:, (nq + nkv) * d:], x[:, (nq + nkv) * d:])  # values and the rest are not touched
 
 
-@pytest.mark.parametrize("dtype,bound", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-def test_recurrent_unit_carries_its_state_across_portions(dtype, bound):
+SHORT_CUTS = ({0: 23, 1: 9}, [(1, 2), (2, 1), (7, 0), (1, 1), (3, 5), (9, 0)])
+LONG_CUTS = ({0: 331, 1: 70}, [(130, 65), (1, 0), (200, 5)])     # long portions: chunks walked side by side
+
+
+@pytest.mark.parametrize("dtype,bound,plan", [(torch.float32, 1e-5, SHORT_CUTS), (torch.bfloat16, 2e-2, SHORT_CUTS),
+                                              (torch.float32, 1e-5, LONG_CUTS), (torch.bfloat16, 2e-2, LONG_CUTS)])
+def test_recurrent_unit_carries_its_state_across_portions(dtype, bound, plan):
     """Convolution tail and recurrent state through portions of 1, 2 and more tokens, two requests
     in one launch, against the plain recurrence over the whole sequence."""
     C, blocks, taps, H = 24, 3, 4, 16
     bw = C // blocks
-    total = {0: 23, 1: 9}
+    total, cuts = plan
     W = {"y": rnd(C, H, seed=20, scale=0.3), "y.b": rnd(C, seed=21, scale=0.1), "x": rnd(C, H, seed=22, scale=0.3),
          "x.b": rnd(C, seed=23, scale=0.1), "conv": rnd(C, taps, seed=24, scale=0.5), "conv.b": rnd(C, seed=25, scale=0.1),
          "ra": rnd(blocks, bw, bw, seed=26, scale=0.4), "ra.b": rnd(blocks, bw, seed=27, scale=0.1),
@@ -269,7 +274,6 @@ def test_recurrent_unit_carries_its_state_across_portions(dtype, bound):
     f32 = lambda t: t.float().to(DEV).contiguous()
     done = {0: 0, 1: 0}
     got = {r: [] for r in total}
-    cuts = [(1, 2), (2, 1), (7, 0), (1, 1), (3, 5), (9, 0)]
     for n0, n1 in cuts:
         lens = [n for n in (n0, n1) if n]
         who = [r for r, n in ((0, n0), (1, n1)) if n]
