@@ -7,6 +7,7 @@
 //                     pos, offsets[E + 1], and the list of row tiles (expert, first row, rows) that the
 //                     grouped products walk.  Nothing comes back to the host: the products are launched
 //                     for the largest possible number of tiles and the surplus blocks leave at once.
+//                     Tiles have 64 rows, or 8 for steps that bring an expert only a few rows.
 //   mi_moe_gate_up    act[pos, :] = glu(W_gate[e] x_token, W_up[e] x_token) for the entries of each expert
 //   mi_moe_down       y[pos, :] = W_down[e] act[pos, :]   (fp32)
 //   mi_moe_combine    out[t, :] = T(sum_k weight[t, k] * y[inv[t*top + k], :] + shared[t, :])
@@ -100,7 +101,7 @@ extern "C" int mi_moe_select(const float* logits, int stride, int* ids, float* w
 
 // plan layout (int32): [0] number of tiles, [1 .. E+1] offsets, then 3 ints per tile (expert, first row, rows)
 __global__ void moe_plan_kernel(const int* __restrict__ ids, int n, int E, int* __restrict__ perm,
-                                int* __restrict__ inv, int* __restrict__ plan) {
+                                int* __restrict__ inv, int* __restrict__ plan, int tile_rows) {
   mi_pdl_enter();
   extern __shared__ int sh[];
   int* counts = sh;            // [E]
@@ -117,10 +118,10 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int n, int E, int* 
       offsets[e] = run;
       cursor[e] = run;
       const int end = run + counts[e];
-      for (int r0 = run; r0 < end; r0 += TILE_M) {
+      for (int r0 = run; r0 < end; r0 += tile_rows) {
         tiles[3 * nt] = e;
         tiles[3 * nt + 1] = r0;
-        tiles[3 * nt + 2] = min(TILE_M, end - r0);
+        tiles[3 * nt + 2] = min(tile_rows, end - r0);
         ++nt;
       }
       run = end;
@@ -136,12 +137,16 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int n, int E, int* 
   }
 }
 
-extern "C" int mi_moe_tile_rows() { return TILE_M; }
+#define FEW_ROWS 8
+// rows per tile: TILE_M for the tiled products, FEW_ROWS for the streaming ones (few rows per expert)
+extern "C" int mi_moe_tile_rows(int few) { return few ? FEW_ROWS : TILE_M; }
 
-extern "C" int mi_moe_plan(const int* ids, int n, int E, int* perm, int* inv, int* plan, cudaStream_t stream) {
+extern "C" int mi_moe_plan(const int* ids, int n, int E, int* perm, int* inv, int* plan, int tile_rows,
+                           cudaStream_t stream) {
   if (n <= 0) return 0;
   if (E <= 0 || E > 4096) MI_REFUSE("moe: %d experts", E);
-  MI_LAUNCH((moe_plan_kernel), 1, 1024, 2 * E * sizeof(int), stream, ids, n, E, perm, inv, plan);
+  if (tile_rows != TILE_M && tile_rows != FEW_ROWS) MI_REFUSE("moe: tiles of %d rows", tile_rows);
+  MI_LAUNCH((moe_plan_kernel), 1, 1024, 2 * E * sizeof(int), stream, ids, n, E, perm, inv, plan, tile_rows);
   MI_RETURN_LAUNCH_STATUS();
 }
 
@@ -362,14 +367,91 @@ static int mma_vec_ok(const void* a, long long a_stride, const void* w0, const v
   return K % 8 == 0 && a_stride % 8 == 0 && mi_aligned(a, 16) && mi_aligned(w0, 16) && (!w1 || mi_aligned(w1, 16));
 }
 
-static int max_tiles(int n_entries, int E) { return (n_entries + TILE_M - 1) / TILE_M + E; }
+// ------------------------------------------------------------------------------------------ few rows per expert
+// A decode step brings an expert a handful of rows: the product is a stream of that expert's weights.
+// Tiles have at most FEW_ROWS rows; a warp owns one output column, its lanes walk k in 16-byte pieces
+// (several loads in flight per lane), the tile's rows of x come through the L1, and the lanes' sums
+// are added at the end.  bfloat16, k a multiple of 8, 16-byte aligned rows.
+__device__ __forceinline__ void fma8(float& acc, const uint4& w, const uint4& x) {
+  const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&w);
+  const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 wf = __bfloat1622float2(wp[i]), xf = __bfloat1622float2(xp[i]);
+    acc = fmaf(wf.x, xf.x, acc);
+    acc = fmaf(wf.y, xf.y, acc);
+  }
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(256)
+moe_stream_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restrict__ w0, const bf16* __restrict__ w1,
+                  long long w_expert_stride, const int* __restrict__ perm, int top, const int* __restrict__ plan,
+                  int E, void* __restrict__ out_, int N, int K, float limit, float alpha) {
+  mi_pdl_enter();
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int* td = plan + 2 + E + 3 * tile;
+  const int e = td[0], row0 = td[1], rows = td[2];
+  __shared__ const bf16* aptr[FEW_ROWS];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < FEW_ROWS)
+    aptr[tid] = tid < rows ? a + (size_t)(GATED ? perm[row0 + tid] / top : row0 + tid) * a_stride : nullptr;
+  __syncthreads();
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const bf16* wr0 = w0 + (size_t)e * w_expert_stride + (size_t)n * K;
+  const bf16* wr1 = GATED ? w1 + (size_t)e * w_expert_stride + (size_t)n * K : nullptr;
+  float acc0[FEW_ROWS], acc1[FEW_ROWS];
+#pragma unroll
+  for (int r = 0; r < FEW_ROWS; ++r) acc0[r] = acc1[r] = 0.f;
+#pragma unroll 4
+  for (int k = lane * 8; k < K; k += 256) {
+    const uint4 wv0 = *reinterpret_cast<const uint4*>(wr0 + k);
+    uint4 wv1 = make_uint4(0u, 0u, 0u, 0u);
+    if (GATED) wv1 = *reinterpret_cast<const uint4*>(wr1 + k);
+#pragma unroll
+    for (int r = 0; r < FEW_ROWS; ++r) {
+      if (r < rows) {
+        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(aptr[r] + k));
+        fma8(acc0[r], wv0, xv);
+        if (GATED) fma8(acc1[r], wv1, xv);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < FEW_ROWS; ++r) {
+    if (r < rows) {
+      const float s0 = mi_warp_sum(acc0[r]);
+      const float s1 = GATED ? mi_warp_sum(acc1[r]) : 0.f;
+      if (lane == 0) {
+        if (GATED)
+          reinterpret_cast<bf16*>(out_)[(size_t)(row0 + r) * N + n] =
+              __float2bfloat16_rn(mi_clamped_glu_value(s0, s1, limit, alpha));
+        else
+          reinterpret_cast<float*>(out_)[(size_t)(row0 + r) * N + n] = s0;
+      }
+    }
+  }
+}
+
+static int max_tiles(int n_entries, int E, int tile_rows) { return (n_entries + tile_rows - 1) / tile_rows + E; }
 
 extern "C" int mi_moe_gate_up(const void* x, int x_stride, const void* w_gate, const void* w_up,
                               long long w_expert_stride, const int* perm, int top, const int* plan, int E,
-                              void* act, int n_entries, int ff, int H, float limit, float alpha, int dtype,
-                              cudaStream_t stream) {
+                              void* act, int n_entries, int ff, int H, float limit, float alpha, int tile_rows,
+                              int dtype, cudaStream_t stream) {
   if (n_entries <= 0) return 0;
-  dim3 grid((ff + TILE_N - 1) / TILE_N, max_tiles(n_entries, E));
+  if (tile_rows == FEW_ROWS) {
+    if (dtype != MI_DTYPE_BF16 || !mma_vec_ok(x, x_stride, w_gate, w_up, H))
+      MI_REFUSE("moe: the streaming product takes bfloat16 rows of whole 16-byte pieces");
+    dim3 g((ff + 7) / 8, max_tiles(n_entries, E, FEW_ROWS));
+    if (g.y > 65535) MI_REFUSE("moe: too many row tiles for one launch");
+    MI_LAUNCH((moe_stream_kernel<true>), g, 256, 0, stream, (const bf16*)x, x_stride, (const bf16*)w_gate,
+              (const bf16*)w_up, w_expert_stride, perm, top, plan, E, act, ff, H, limit, alpha);
+    MI_RETURN_LAUNCH_STATUS();
+  }
+  dim3 grid((ff + TILE_N - 1) / TILE_N, max_tiles(n_entries, E, TILE_M));
   if (grid.y > 65535) MI_REFUSE("moe: too many row tiles for one launch");
   if (dtype == MI_DTYPE_F32)
     MI_LAUNCH((moe_gemm_kernel<float, true>), grid, 256, 0, stream, (const float*)x, x_stride, (const float*)w_gate,
@@ -384,9 +466,18 @@ extern "C" int mi_moe_gate_up(const void* x, int x_stride, const void* w_gate, c
 }
 
 extern "C" int mi_moe_down(const void* act, const void* w_down, long long w_expert_stride, const int* plan, int E,
-                           float* y, int n_entries, int H, int ff, int dtype, cudaStream_t stream) {
+                           float* y, int n_entries, int H, int ff, int tile_rows, int dtype, cudaStream_t stream) {
   if (n_entries <= 0) return 0;
-  dim3 grid((H + TILE_N - 1) / TILE_N, max_tiles(n_entries, E));
+  if (tile_rows == FEW_ROWS) {
+    if (dtype != MI_DTYPE_BF16 || !mma_vec_ok(act, ff, w_down, nullptr, ff))
+      MI_REFUSE("moe: the streaming product takes bfloat16 rows of whole 16-byte pieces");
+    dim3 g((H + 7) / 8, max_tiles(n_entries, E, FEW_ROWS));
+    if (g.y > 65535) MI_REFUSE("moe: too many row tiles for one launch");
+    MI_LAUNCH((moe_stream_kernel<false>), g, 256, 0, stream, (const bf16*)act, ff, (const bf16*)w_down,
+              (const bf16*)nullptr, w_expert_stride, (const int*)nullptr, 1, plan, E, (void*)y, H, ff, 0.f, 0.f);
+    MI_RETURN_LAUNCH_STATUS();
+  }
+  dim3 grid((H + TILE_N - 1) / TILE_N, max_tiles(n_entries, E, TILE_M));
   if (grid.y > 65535) MI_REFUSE("moe: too many row tiles for one launch");
   if (dtype == MI_DTYPE_F32)
     MI_LAUNCH((moe_gemm_kernel<float, false>), grid, 256, 0, stream, (const float*)act, ff, (const float*)w_down,

@@ -241,11 +241,12 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
 def _sig_moe(lib: ctypes.CDLL) -> None:
     ll = ctypes.c_longlong
     lib.mi_moe_select.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
-    lib.mi_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.mi_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+    lib.mi_moe_tile_rows.argtypes = [c_int]
     lib.mi_moe_tile_rows.restype = c_int
     lib.mi_moe_gate_up.argtypes = [c_void_p, c_int, c_void_p, c_void_p, ll, c_void_p, c_int, c_void_p, c_int,
-                                   c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]
-    lib.mi_moe_down.argtypes = [c_void_p, c_void_p, ll, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                   c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p]
+    lib.mi_moe_down.argtypes = [c_void_p, c_void_p, ll, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                 c_void_p]
     lib.mi_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                    c_int, c_void_p]
@@ -1367,6 +1368,9 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, top: int) -> tuple[torch.Te
     return ids, weights
 
 
+MOE_FEW_ROWS_PER_EXPERT = 8     # up to this many rows per expert on average: the streaming products
+
+
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
                 w_down: torch.Tensor, limit: float, alpha: float, shared: torch.Tensor | None = None) -> torch.Tensor:
     """``out[t] = sum_k weights[t, k] * expert_{ids[t, k]}(x[t]) (+ shared[t])`` with
@@ -1391,19 +1395,24 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
             raise KernelError("moe: the shared expert's output must be [M, H] in x's dtype")
     n = M * top
     lib = _lib("moe")
-    tile = lib.mi_moe_tile_rows()
+    # a step that brings an expert a few rows streams the weights (tiles of 8 rows, a warp per output
+    # column); otherwise tiles of 64 rows on the tensor cores (float32: on CUDA cores)
+    few = (x.dtype == torch.bfloat16 and n <= MOE_FEW_ROWS_PER_EXPERT * E and H % 8 == 0 and ff % 8 == 0
+           and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+    tile = lib.mi_moe_tile_rows(1 if few else 0)
     dev = x.device
     perm = torch.empty(n, dtype=torch.int32, device=dev)
     inv = torch.empty(n, dtype=torch.int32, device=dev)
     plan = torch.empty(2 + E + 3 * (-(-n // tile) + E), dtype=torch.int32, device=dev)
-    rc = lib.mi_moe_plan(_ptr(ids), n, E, _ptr(perm), _ptr(inv), _ptr(plan), _stream())
+    rc = lib.mi_moe_plan(_ptr(ids), n, E, _ptr(perm), _ptr(inv), _ptr(plan), tile, _stream())
     _finish(lib, rc, "moe_plan")
     act = torch.empty((n, ff), dtype=x.dtype, device=dev)
     rc = lib.mi_moe_gate_up(_ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), ff * H, _ptr(perm), top, _ptr(plan), E,
-                            _ptr(act), n, ff, H, float(limit), float(alpha), _code(x.dtype), _stream())
+                            _ptr(act), n, ff, H, float(limit), float(alpha), tile, _code(x.dtype), _stream())
     _finish(lib, rc, "moe_gate_up")
     y = torch.empty((n, H), dtype=torch.float32, device=dev)
-    rc = lib.mi_moe_down(_ptr(act), _ptr(w_down), H * ff, _ptr(plan), E, _ptr(y), n, H, ff, _code(x.dtype), _stream())
+    rc = lib.mi_moe_down(_ptr(act), _ptr(w_down), H * ff, _ptr(plan), E, _ptr(y), n, H, ff, tile, _code(x.dtype),
+                         _stream())
     _finish(lib, rc, "moe_down")
     out = torch.empty((M, H), dtype=x.dtype, device=dev)
     rc = lib.mi_moe_combine(_ptr(y), _ptr(inv), _ptr(weights), _ptr(shared), shared.stride(0) if shared is not None else 0,

@@ -298,8 +298,8 @@ extern "C" int mi_rglru_scan_chunked(const float* gates, int M, int bw, const fl
 #define GLA_R 8
 #define GLA_L 16
 
-template <typename T>
-__global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int stride,
+template <typename T, int MAXT>
+__global__ void __launch_bounds__(MAXT) gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int stride,
                                 const float* __restrict__ z, int z_stride, const float* __restrict__ z_bias,
                                 float inv_tau, float q_scale, float* __restrict__ state, long long state_stride,
                                 const int* __restrict__ q_start, const int* __restrict__ q_len,
@@ -324,23 +324,55 @@ __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k
     const int kk = ty * GLA_R + i;
     s[i] = (kk < dk && j < dv) ? S[(size_t)kk * dv + j] : 0.f;
   }
+  // A group's q, k, z and v are fetched into registers while the group before is worked on, so that
+  // the walk does not stand still for a round trip to memory at every group.
+  // Per thread at most 4 elements of each of q, k, z (GLA_L * dk / threads <= 4) and 4 of v (at least
+  // 128 threads).
+  float pq[4], pk[4], pz[4], pv[4];
+  auto fetch = [&](int t0) {
+    const int n = min(GLA_L, len - t0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * nthreads;
+      if (idx < n * dk) {
+        const int l = idx / dk, kk = idx - l * dk;
+        const size_t m = (size_t)(row0 + t0 + l);
+        pq[i] = mi_to_float(q[m * stride + head * dk + kk]);
+        pk[i] = mi_to_float(k[m * stride + head * dk + kk]);
+        pz[i] = z[m * z_stride + head * dk + kk];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * nthreads;
+      if (idx < n * 32) {
+        const int l = idx >> 5, jj = blockIdx.x * 32 + (idx & 31);
+        pv[i] = jj < dv ? mi_to_float(v[(size_t)(row0 + t0 + l) * stride + head * dv + jj]) : 0.f;
+      }
+    }
+  };
+  if (len > 0) fetch(0);
   for (int t0 = 0; t0 < len; t0 += GLA_L) {
     const int n = min(GLA_L, len - t0);
     __syncthreads();   // the group before is consumed
-    for (int idx = tid; idx < n * dk; idx += nthreads) {
-      const int l = idx / dk, kk = idx - l * dk;
-      const size_t m = (size_t)(row0 + t0 + l);
-      qs[l * dk + kk] = mi_to_float(q[m * stride + head * dk + kk]) * q_scale;
-      ks[l * dk + kk] = mi_to_float(k[m * stride + head * dk + kk]);
-      const float zz = z[m * z_stride + head * dk + kk] + (z_bias ? z_bias[head * dk + kk] : 0.f);
-      // sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau)
-      as[l * dk + kk] = expf(-mi_softplus(-zz) * inv_tau);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * nthreads;
+      if (idx < n * dk) {
+        const int kk = idx % dk;
+        qs[idx] = pq[i] * q_scale;
+        ks[idx] = pk[i];
+        const float zz = pz[i] + (z_bias ? z_bias[head * dk + kk] : 0.f);
+        as[idx] = expf(-mi_softplus(-zz) * inv_tau);     // sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau)
+      }
     }
-    for (int idx = tid; idx < n * 32; idx += nthreads) {
-      const int l = idx >> 5, jj = blockIdx.x * 32 + (idx & 31);
-      vs[idx] = jj < dv ? mi_to_float(v[(size_t)(row0 + t0 + l) * stride + head * dv + jj]) : 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * nthreads;
+      if (idx < n * 32) vs[idx] = pv[i];
     }
     __syncthreads();
+    if (t0 + GLA_L < len) fetch(t0 + GLA_L);
     for (int l = 0; l < n; ++l) {
       const float vv = vs[l * 32 + tx];
       float po = 0.f;
@@ -375,12 +407,12 @@ extern "C" int mi_gla_scan(const void* q, const void* k, const void* v, int stri
   if (n_requests <= 0) return 0;
   if (dk <= 0 || dk > 256 || dv <= 0) MI_REFUSE("gla: key size %d must lie in [1, 256], value size %d above 0", dk, dv);
   if (heads > 65535 || n_requests > 65535) MI_REFUSE("gla: too many heads or requests for one launch");
-  const int KP = (dk + GLA_R - 1) / GLA_R;
+  const int KP = max(4, (dk + GLA_R - 1) / GLA_R);     // at least 128 threads: they also stage the inputs
   dim3 grid((dv + 31) / 32, heads, n_requests), block(32, KP);
   const size_t smem = ((size_t)3 * GLA_L * dk + GLA_L * 32 + (size_t)GLA_L * KP * 32) * sizeof(float);
 #define MI_GO(T)                                                                                          \
   do {                                                                                                    \
-    auto kern = gla_scan_kernel<T>;                                                                       \
+    auto kern = KP <= 16 ? gla_scan_kernel<T, 512> : gla_scan_kernel<T, 1024>;                            \
     if (smem > 48 * 1024) {                                                                               \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return (int)e;                                                                \

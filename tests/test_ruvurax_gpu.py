@@ -340,7 +340,8 @@ def test_gated_linear_attention_state(heads, dk, dv):
     assert (out.cpu().double() - ref).abs().max() <= 1e-5 * max(1.0, ref.abs().max())
 
 
-@pytest.mark.parametrize("E,top,ff,H,M", [(5, 2, 24, 40, 33), (3, 1, 20, 48, 5), (4, 4, 16, 36, 70), (12, 3, 72, 64, 200)])
+@pytest.mark.parametrize("E,top,ff,H,M", [(5, 2, 24, 40, 33), (3, 1, 20, 48, 5), (4, 4, 16, 36, 70), (12, 3, 72, 64, 200),
+                                          (6, 2, 24, 40, 7), (3, 3, 16, 64, 8), (16, 1, 8, 264, 100)])
 @pytest.mark.parametrize("dtype,bound", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
 def test_routed_experts(E, top, ff, H, M, dtype, bound):
     """Router choice and weights, the clamped activation, and the weighted sum, against the plain
