@@ -10,6 +10,7 @@
 //                     Tiles have 64 rows, or 8 for steps that bring an expert only a few rows.
 //   mi_moe_gate_up    act[pos, :] = glu(W_gate[e] x_token, W_up[e] x_token) for the entries of each expert
 //   mi_moe_down       y[pos, :] = W_down[e] act[pos, :]   (fp32)
+//   mi_moe_gather     xs[pos, :] = x[token of pos, :], for steps whose products are a library's grouped product
 //   mi_moe_combine    out[t, :] = T(sum_k weight[t, k] * y[inv[t*top + k], :] + shared[t, :])
 //   mi_clamped_glu    the same activation for a dense expert: out = glu(gu[:, :I], gu[:, I:])
 //
@@ -491,9 +492,41 @@ extern "C" int mi_moe_down(const void* act, const void* w_down, long long w_expe
   MI_RETURN_LAUNCH_STATUS();
 }
 
-// ------------------------------------------------------------------------------------------ combine
+// ------------------------------------------------------------------------------------------ gather, combine
+// xs[pos, :] = x[perm[pos] / top, :]: an expert's rows side by side, for a library's grouped product
 template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ inv,
+__global__ void moe_gather_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__ perm, int top,
+                                  T* __restrict__ xs, int H, int vec) {
+  mi_pdl_enter();
+  const int pos = blockIdx.x;
+  const T* src = x + (size_t)(perm[pos] / top) * x_stride;
+  T* dst = xs + (size_t)pos * H;
+  if (vec) {
+    constexpr int EPC = 16 / (int)sizeof(T);
+    for (int c = threadIdx.x * EPC; c < H; c += blockDim.x * EPC)
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+  } else {
+    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = src[c];
+  }
+}
+
+extern "C" int mi_moe_gather(const void* x, int x_stride, const int* perm, int top, void* xs, int n, int H, int dtype,
+                             cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int es = dtype == MI_DTYPE_F32 ? 4 : 2;
+  const int epc = 16 / es;
+  const int vec = (H % epc == 0) && (x_stride % epc == 0) && mi_aligned(x, 16) && mi_aligned(xs, 16);
+  if (dtype == MI_DTYPE_F32)
+    MI_LAUNCH((moe_gather_kernel<float>), n, 128, 0, stream, (const float*)x, x_stride, perm, top, (float*)xs, H, vec);
+  else if (dtype == MI_DTYPE_BF16)
+    MI_LAUNCH((moe_gather_kernel<bf16>), n, 128, 0, stream, (const bf16*)x, x_stride, perm, top, (bf16*)xs, H, vec);
+  else
+    MI_REFUSE("moe: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+template <typename T, typename YT>
+__global__ void moe_combine_kernel(const YT* __restrict__ y, const int* __restrict__ inv,
                                    const float* __restrict__ weights, const T* __restrict__ shared, int shared_stride,
                                    T* __restrict__ out, int H, int top) {
   mi_pdl_enter();
@@ -501,24 +534,28 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k)
-      acc = fmaf(weights[(size_t)t * top + k], y[(size_t)inv[(size_t)t * top + k] * H + c], acc);
+      acc = fmaf(weights[(size_t)t * top + k], mi_to_float(y[(size_t)inv[(size_t)t * top + k] * H + c]), acc);
     if (shared) acc += mi_to_float(shared[(size_t)t * shared_stride + c]);
     out[(size_t)t * H + c] = mi_from_float<T>(acc);
   }
 }
 
-extern "C" int mi_moe_combine(const float* y, const int* inv, const float* weights, const void* shared,
+// y_dtype: the experts' outputs are fp32 (own products) or in the compute dtype (a library's grouped product)
+extern "C" int mi_moe_combine(const void* y, int y_dtype, const int* inv, const float* weights, const void* shared,
                               int shared_stride, void* out, int M, int H, int top, int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
-  if (dtype == MI_DTYPE_F32)
-    MI_LAUNCH((moe_combine_kernel<float>), M, threads, 0, stream, y, inv, weights, (const float*)shared,
-              shared_stride, (float*)out, H, top);
-  else if (dtype == MI_DTYPE_BF16)
-    MI_LAUNCH((moe_combine_kernel<bf16>), M, threads, 0, stream, y, inv, weights, (const bf16*)shared,
-              shared_stride, (bf16*)out, H, top);
+  if (dtype == MI_DTYPE_F32 && y_dtype == MI_DTYPE_F32)
+    MI_LAUNCH((moe_combine_kernel<float, float>), M, threads, 0, stream, (const float*)y, inv, weights,
+              (const float*)shared, shared_stride, (float*)out, H, top);
+  else if (dtype == MI_DTYPE_BF16 && y_dtype == MI_DTYPE_F32)
+    MI_LAUNCH((moe_combine_kernel<bf16, float>), M, threads, 0, stream, (const float*)y, inv, weights,
+              (const bf16*)shared, shared_stride, (bf16*)out, H, top);
+  else if (dtype == MI_DTYPE_BF16 && y_dtype == MI_DTYPE_BF16)
+    MI_LAUNCH((moe_combine_kernel<bf16, bf16>), M, threads, 0, stream, (const bf16*)y, inv, weights,
+              (const bf16*)shared, shared_stride, (bf16*)out, H, top);
   else
-    MI_REFUSE("moe: unknown dtype %d", dtype);
+    MI_REFUSE("moe: unsupported dtypes %d (activations) and %d (expert outputs)", dtype, y_dtype);
   MI_RETURN_LAUNCH_STATUS();
 }
 

@@ -248,8 +248,9 @@ def _sig_moe(lib: ctypes.CDLL) -> None:
                                    c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p]
     lib.mi_moe_down.argtypes = [c_void_p, c_void_p, ll, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                 c_void_p]
-    lib.mi_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+    lib.mi_moe_combine.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                    c_int, c_void_p]
+    lib.mi_moe_gather.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
     lib.mi_clamped_glu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]
 
 
@@ -1369,23 +1370,30 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, top: int) -> tuple[torch.Te
 
 
 MOE_FEW_ROWS_PER_EXPERT = 8     # up to this many rows per expert on average: the streaming products
+USE_GROUPED_MM = os.environ.get("MINI_INFER_GROUPED_MM", "1") != "0"
 
 
-def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
                 w_down: torch.Tensor, limit: float, alpha: float, shared: torch.Tensor | None = None) -> torch.Tensor:
     """``out[t] = sum_k weights[t, k] * expert_{ids[t, k]}(x[t]) (+ shared[t])`` with
     ``expert(x) = W_down glu(W_gate x, W_up x)``, ``glu(g, u) = g' sigmoid(alpha g') (u' + 1)``,
     ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``.  Weights are stacked per expert:
-    ``w_gate, w_up [E, ff, H]``, ``w_down [E, H, ff]``.  Entries are sorted by expert on the
-    device and the products walk tiles of one expert's rows; nothing is read back."""
-    _cuda(x, ids, weights, w_gate, w_up, w_down, shared)
+    ``w_gate_up [E, 2 ff, H]`` (an expert's gate rows, then its up rows), ``w_down [E, H, ff]``.
+    Entries are sorted by expert on the device; nothing is read back.  Three routes: a step that
+    brings an expert only a few rows streams the weights (bfloat16); large bfloat16 steps gather
+    each expert's rows and use the library's grouped product (as the dense layers use the library's
+    product for many rows); everything else walks 64-row tiles with this module's own kernels
+    (tensor cores for bfloat16, CUDA cores with a fixed summation order for float32)."""
+    global launch_count
+    _cuda(x, ids, weights, w_gate_up, w_down, shared)
     _cols(x, "moe")
     M, H = x.shape
-    E, ff, _ = w_gate.shape
+    E, ff2, _ = w_gate_up.shape
+    ff = ff2 // 2
     top = ids.shape[1]
-    for w, shape in ((w_gate, (E, ff, H)), (w_up, (E, ff, H)), (w_down, (E, H, ff))):
+    for w, shape in ((w_gate_up, (E, 2 * ff, H)), (w_down, (E, H, ff))):
         if tuple(w.shape) != shape or w.dtype != x.dtype or not w.is_contiguous():
-            raise KernelError("moe: expert weights must be contiguous [E, ff, H], [E, ff, H], [E, H, ff] in x's dtype")
+            raise KernelError("moe: expert weights must be contiguous [E, 2 ff, H] and [E, H, ff] in x's dtype")
     if ids.dtype != torch.int32 or weights.dtype != torch.float32 or ids.shape != weights.shape or ids.shape[0] != M \
             or not ids.is_contiguous() or not weights.is_contiguous():
         raise KernelError("moe: ids int32 [M, top] and weights fp32 [M, top]")
@@ -1395,10 +1403,10 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
             raise KernelError("moe: the shared expert's output must be [M, H] in x's dtype")
     n = M * top
     lib = _lib("moe")
-    # a step that brings an expert a few rows streams the weights (tiles of 8 rows, a warp per output
-    # column); otherwise tiles of 64 rows on the tensor cores (float32: on CUDA cores)
-    few = (x.dtype == torch.bfloat16 and n <= MOE_FEW_ROWS_PER_EXPERT * E and H % 8 == 0 and ff % 8 == 0
-           and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+    pieces = (x.dtype == torch.bfloat16 and H % 8 == 0 and ff % 8 == 0 and x.stride(0) % 8 == 0
+              and x.data_ptr() % 16 == 0)          # rows are whole 16-byte pieces
+    few = pieces and n <= MOE_FEW_ROWS_PER_EXPERT * E
+    grouped = pieces and not few and USE_GROUPED_MM and hasattr(torch, "_grouped_mm")
     tile = lib.mi_moe_tile_rows(1 if few else 0)
     dev = x.device
     perm = torch.empty(n, dtype=torch.int32, device=dev)
@@ -1406,17 +1414,28 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     plan = torch.empty(2 + E + 3 * (-(-n // tile) + E), dtype=torch.int32, device=dev)
     rc = lib.mi_moe_plan(_ptr(ids), n, E, _ptr(perm), _ptr(inv), _ptr(plan), tile, _stream())
     _finish(lib, rc, "moe_plan")
-    act = torch.empty((n, ff), dtype=x.dtype, device=dev)
-    rc = lib.mi_moe_gate_up(_ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), ff * H, _ptr(perm), top, _ptr(plan), E,
-                            _ptr(act), n, ff, H, float(limit), float(alpha), tile, _code(x.dtype), _stream())
-    _finish(lib, rc, "moe_gate_up")
-    y = torch.empty((n, H), dtype=torch.float32, device=dev)
-    rc = lib.mi_moe_down(_ptr(act), _ptr(w_down), H * ff, _ptr(plan), E, _ptr(y), n, H, ff, tile, _code(x.dtype),
-                         _stream())
-    _finish(lib, rc, "moe_down")
+    if grouped:
+        xs = torch.empty((n, H), dtype=x.dtype, device=dev)
+        rc = lib.mi_moe_gather(_ptr(x), x.stride(0), _ptr(perm), top, _ptr(xs), n, H, _code(x.dtype), _stream())
+        _finish(lib, rc, "moe_gather")
+        ends = plan[2:2 + E]                       # where each expert's rows end
+        act = clamped_glu(torch._grouped_mm(xs, w_gate_up.transpose(-2, -1), offs=ends), limit, alpha)
+        y = torch._grouped_mm(act, w_down.transpose(-2, -1), offs=ends)
+        launch_count += 2
+    else:
+        act = torch.empty((n, ff), dtype=x.dtype, device=dev)
+        rc = lib.mi_moe_gate_up(_ptr(x), x.stride(0), _ptr(w_gate_up), _ptr(w_gate_up[:, ff:]), 2 * ff * H, _ptr(perm),
+                                top, _ptr(plan), E, _ptr(act), n, ff, H, float(limit), float(alpha), tile,
+                                _code(x.dtype), _stream())
+        _finish(lib, rc, "moe_gate_up")
+        y = torch.empty((n, H), dtype=torch.float32, device=dev)
+        rc = lib.mi_moe_down(_ptr(act), _ptr(w_down), H * ff, _ptr(plan), E, _ptr(y), n, H, ff, tile, _code(x.dtype),
+                             _stream())
+        _finish(lib, rc, "moe_down")
     out = torch.empty((M, H), dtype=x.dtype, device=dev)
-    rc = lib.mi_moe_combine(_ptr(y), _ptr(inv), _ptr(weights), _ptr(shared), shared.stride(0) if shared is not None else 0,
-                            _ptr(out), M, H, top, _code(x.dtype), _stream())
+    rc = lib.mi_moe_combine(_ptr(y), _code(y.dtype), _ptr(inv), _ptr(weights), _ptr(shared),
+                            shared.stride(0) if shared is not None else 0, _ptr(out), M, H, top, _code(x.dtype),
+                            _stream())
     _finish(lib, rc, "moe_combine")
     return out
 

@@ -53,8 +53,9 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors, dtype, device):
         E = range(self.experts)
         self.router = _as_compute(tensors["router"], dtype).contiguous()
-        self.w_gate = torch.stack([_as_compute(tensors[f"e{e}.gate"], dtype) for e in E]).contiguous()
-        self.w_up = torch.stack([_as_compute(tensors[f"e{e}.up"], dtype) for e in E]).contiguous()
+        # per expert its gate rows, then its up rows: one operand for a grouped product, two for the own kernels
+        self.w_gate_up = torch.stack([torch.cat([_as_compute(tensors[f"e{e}.gate"], dtype),
+                                                 _as_compute(tensors[f"e{e}.up"], dtype)]) for e in E]).contiguous()
         self.w_down = torch.stack([_as_compute(tensors[f"e{e}.down"], dtype) for e in E]).contiguous()
         self.shared_in = self.shared_out = None
         if self.shared_ff:
@@ -67,7 +68,7 @@ class RoutedExperts(FeedForward):
         if self.shared_in is not None:
             shared = self.shared_out(ops.clamped_glu(self.shared_in(x), self.shared_limit, self.alpha))
         ids, weights = ops.moe_route(x, self.router, self.top)
-        return ops.moe_experts(x, ids, weights, self.w_gate, self.w_up, self.w_down, self.limit, self.alpha, shared)
+        return ops.moe_experts(x, ids, weights, self.w_gate_up, self.w_down, self.limit, self.alpha, shared)
 
 
 register_feed_forward("routed_experts", RoutedExperts, replace=True)

@@ -362,9 +362,10 @@ def test_routed_experts(E, top, ff, H, M, dtype, bound):
     vals, idx = torch.topk(z, top, dim=-1)
     assert torch.equal(ids.cpu().long()[ok], idx[ok])
     assert (wts.cpu().double()[ok] - torch.softmax(vals, dim=-1)[ok]).abs().max() < 1e-5
-    stack = lambda n: torch.stack([W[f"e{e}.{n}"] for e in range(E)]).to(DEV).contiguous()
+    gate_up = torch.stack([torch.cat([W[f"e{e}.gate"], W[f"e{e}.up"]]) for e in range(E)]).to(DEV).contiguous()
+    down = torch.stack([W[f"e{e}.down"] for e in range(E)]).to(DEV).contiguous()
     shared = rnd(M, H, seed=62).to(dtype)
-    out = ops().moe_experts(dx, ids, wts, stack("gate"), stack("up"), stack("down"), 0.9, 1.702, shared.to(DEV))
+    out = ops().moe_experts(dx, ids, wts, gate_up, down, 0.9, 1.702, shared.to(DEV))
     ref = want + shared.double()
     assert (out.cpu().double() - ref)[ok].abs().max() <= bound * max(1.0, ref.abs().max())
 
