@@ -233,7 +233,9 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
     lib.mi_rglru_chunked_scratch.restype = ll
     lib.mi_gla_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
                                 c_void_p, ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                c_int, c_int, c_void_p]
+                                c_int, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mi_gla_chunked_scratch.argtypes = [c_int, c_int, c_int, c_int, c_int]
+    lib.mi_gla_chunked_scratch.restype = ll
     lib.mi_headnorm_gate.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                      c_int, c_float, c_int, c_float, c_int, c_void_p]
 
@@ -1297,6 +1299,9 @@ def rglru_scan(gates: torch.Tensor, gate_bias_r: torch.Tensor, gate_bias_i: torc
     _finish(lib, rc, "rglru")
 
 
+GLA_CHUNK = 128      # tokens per chunk of the chunked walk of gated linear attention
+
+
 def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias: torch.Tensor | None,
              tau: float, q_scale: float, heads: int, dk: int, dv: int, state: torch.Tensor, ctx) -> torch.Tensor:
     """Gated linear attention over each request's portion, from and into its state row
@@ -1319,10 +1324,20 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         raise KernelError("gla: state row too short")
     o = torch.empty((M, heads * dv), dtype=torch.float32, device=q.device)
     lib = _lib("recurrent")
+    longest = _max_q_len(ctx)
+    n_chunks, scratch = 1, None
+    if q.dtype == torch.bfloat16 and longest > GLA_CHUNK:
+        # long portions: chunks side by side, two launches (the float32 path keeps the plain walk, whose
+        # sums do not depend on where a portion starts)
+        global launch_count
+        n_chunks = -(-longest // GLA_CHUNK)
+        scratch = torch.empty(lib.mi_gla_chunked_scratch(ctx.n_requests, n_chunks, heads, dk, dv), dtype=torch.float32,
+                              device=q.device)
+        launch_count += 1
     rc = lib.mi_gla_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(z), z.stride(0), _ptr(z_bias), 1.0 / float(tau),
                          float(q_scale), _ptr(state), stride, _ptr(ctx.q_start), _ptr(ctx.q_len),
-                         _ptr(ctx.state_slot), _ptr(o), o.stride(0), ctx.n_requests, heads, dk, dv, _code(q.dtype),
-                         _stream())
+                         _ptr(ctx.state_slot), _ptr(o), o.stride(0), ctx.n_requests, heads, dk, dv, _ptr(scratch),
+                         n_chunks, GLA_CHUNK, _code(q.dtype), _stream())
     _finish(lib, rc, "gla")
     return o
 

@@ -304,7 +304,13 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const T* __restrict__ q,
                                 float inv_tau, float q_scale, float* __restrict__ state, long long state_stride,
                                 const int* __restrict__ q_start, const int* __restrict__ q_len,
                                 const int* __restrict__ state_slot, float* __restrict__ o, int o_stride,
-                                int heads, int dk, int dv) {
+                                int heads, int dk, int dv, int pass, int chunk_len, int n_chunks,
+                                float* __restrict__ scratch) {
+  // pass 0: the whole portion, from and into the state.  Long portions run as chunks side by side:
+  // pass 1 folds every chunk into (A, B) with S_end = diag(A) S_begin + B (and saves the state the
+  // portion starts from), pass 2 walks the chunks before its own to get S_begin and then its own
+  // tokens as pass 0 does; the last chunk stores the state.
+  // scratch: per (request, chunk, head) A [dk] and B [dk, dv]; then per (request, head) the state at the start.
   mi_pdl_enter();
   extern __shared__ float sm[];
   const int KP = blockDim.y;
@@ -314,15 +320,37 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const T* __restrict__ q,
   float* vs = as + GLA_L * dk;          // [GLA_L][32]
   float* part = vs + GLA_L * 32;        // [GLA_L][KP][32]
   const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * 32 + tx, nthreads = KP * 32;
-  const int head = blockIdx.y, req = blockIdx.z;
+  const int head = blockIdx.y, req = blockIdx.z / n_chunks, chunk = blockIdx.z - req * n_chunks;
   const int j = blockIdx.x * 32 + tx;   // value column
-  const int len = q_len[req], row0 = q_start[req];
+  const int len_all = q_len[req];
+  const int c0 = pass ? chunk * chunk_len : 0;
+  if (c0 >= len_all) return;
+  const int len = (pass ? min(len_all, c0 + chunk_len) : len_all) - c0, row0 = q_start[req] + c0;
+  const bool last = c0 + len == len_all;
   float* S = state + (size_t)state_slot[req] * state_stride + (size_t)head * dk * dv;
-  float s[GLA_R];
+  const size_t unit = (size_t)dk + (size_t)dk * dv;
+  const int n_req = gridDim.z / n_chunks;
+  float* summ = scratch ? scratch + (((size_t)req * n_chunks + chunk) * heads + head) * unit : nullptr;
+  float* begin = scratch ? scratch + (size_t)n_req * n_chunks * heads * unit + ((size_t)req * heads + head) * dk * dv
+                         : nullptr;
+  float s[GLA_R], pa[GLA_R];
 #pragma unroll
   for (int i = 0; i < GLA_R; ++i) {
     const int kk = ty * GLA_R + i;
-    s[i] = (kk < dk && j < dv) ? S[(size_t)kk * dv + j] : 0.f;
+    const bool mine = kk < dk && j < dv;
+    pa[i] = 1.f;
+    if (pass == 0) {
+      s[i] = mine ? S[(size_t)kk * dv + j] : 0.f;
+    } else if (pass == 1) {
+      s[i] = 0.f;
+      if (chunk == 0 && mine) begin[(size_t)kk * dv + j] = S[(size_t)kk * dv + j];
+    } else {
+      s[i] = mine ? begin[(size_t)kk * dv + j] : 0.f;
+      for (int p = 0; p < chunk; ++p) {
+        const float* ps = scratch + (((size_t)req * n_chunks + p) * heads + head) * unit;
+        if (mine) s[i] = fmaf(ps[kk], s[i], ps[dk + (size_t)kk * dv + j]);
+      }
+    }
   }
   // A group's q, k, z and v are fetched into registers while the group before is worked on, so that
   // the walk does not stand still for a round trip to memory at every group.
@@ -380,14 +408,16 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const T* __restrict__ q,
       for (int i = 0; i < GLA_R; ++i) {
         const int kk = ty * GLA_R + i;
         if (kk < dk) {
-          s[i] = fmaf(as[l * dk + kk], s[i], ks[l * dk + kk] * vv);
-          po = fmaf(s[i], qs[l * dk + kk], po);
+          const float al = as[l * dk + kk];
+          s[i] = fmaf(al, s[i], ks[l * dk + kk] * vv);
+          if (pass == 1) pa[i] *= al;
+          else po = fmaf(s[i], qs[l * dk + kk], po);
         }
       }
-      part[(l * KP + ty) * 32 + tx] = po;
+      if (pass != 1) part[(l * KP + ty) * 32 + tx] = po;
     }
     __syncthreads();
-    for (int l = ty; l < n; l += KP) {
+    if (pass != 1) for (int l = ty; l < n; l += KP) {
       float sum = 0.f;
       for (int p = 0; p < KP; ++p) sum += part[(l * KP + p) * 32 + tx];
       if (j < dv) o[(size_t)(row0 + t0 + l) * o_stride + head * dv + j] = sum;
@@ -396,19 +426,33 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const T* __restrict__ q,
 #pragma unroll
   for (int i = 0; i < GLA_R; ++i) {
     const int kk = ty * GLA_R + i;
+    if (pass == 1) {
+      if (kk < dk && j < dv) summ[dk + (size_t)kk * dv + j] = s[i];
+      if (kk < dk && j == 0) summ[kk] = pa[i];
+      continue;
+    }
+    if (!last) continue;
     if (kk < dk && j < dv) S[(size_t)kk * dv + j] = s[i];
   }
+}
+
+extern "C" long long mi_gla_chunked_scratch(int n_requests, int n_chunks, int heads, int dk, int dv) {
+  const long long unit = (long long)dk + (long long)dk * dv;
+  return (long long)n_requests * n_chunks * heads * unit + (long long)n_requests * heads * dk * dv;
 }
 
 extern "C" int mi_gla_scan(const void* q, const void* k, const void* v, int stride, const float* z, int z_stride,
                            const float* z_bias, float inv_tau, float q_scale, float* state, long long state_stride,
                            const int* q_start, const int* q_len, const int* state_slot, float* o, int o_stride,
-                           int n_requests, int heads, int dk, int dv, int dtype, cudaStream_t stream) {
+                           int n_requests, int heads, int dk, int dv, float* scratch, int n_chunks, int chunk_len,
+                           int dtype, cudaStream_t stream) {
   if (n_requests <= 0) return 0;
+  if (n_chunks < 1 || (n_chunks > 1 && (!scratch || chunk_len <= 0))) MI_REFUSE("gla: chunks need scratch memory");
+  if ((long long)n_requests * n_chunks > 65535) MI_REFUSE("gla: too many chunks for one launch");
   if (dk <= 0 || dk > 256 || dv <= 0) MI_REFUSE("gla: key size %d must lie in [1, 256], value size %d above 0", dk, dv);
   if (heads > 65535 || n_requests > 65535) MI_REFUSE("gla: too many heads or requests for one launch");
   const int KP = max(4, (dk + GLA_R - 1) / GLA_R);     // at least 128 threads: they also stage the inputs
-  dim3 grid((dv + 31) / 32, heads, n_requests), block(32, KP);
+  dim3 grid((dv + 31) / 32, heads, n_requests * n_chunks), block(32, KP);
   const size_t smem = ((size_t)3 * GLA_L * dk + GLA_L * 32 + (size_t)GLA_L * KP * 32) * sizeof(float);
 #define MI_GO(T)                                                                                          \
   do {                                                                                                    \
@@ -417,8 +461,10 @@ extern "C" int mi_gla_scan(const void* q, const void* k, const void* v, int stri
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return (int)e;                                                                \
     }                                                                                                     \
-    MI_LAUNCH(kern, grid, block, smem, stream, (const T*)q, (const T*)k, (const T*)v, stride, z, z_stride,  \
-              z_bias, inv_tau, q_scale, state, state_stride, q_start, q_len, state_slot, o, o_stride, heads, dk, dv); \
+    for (int pass = n_chunks > 1 ? 1 : 0; pass <= (n_chunks > 1 ? 2 : 0); ++pass)                         \
+      MI_LAUNCH(kern, grid, block, smem, stream, (const T*)q, (const T*)k, (const T*)v, stride, z, z_stride, \
+                z_bias, inv_tau, q_scale, state, state_stride, q_start, q_len, state_slot, o, o_stride, heads, \
+                dk, dv, pass, chunk_len, n_chunks, scratch);                                               \
   } while (0)
   if (dtype == MI_DTYPE_F32) MI_GO(float);
   else if (dtype == MI_DTYPE_BF16) MI_GO(bf16);

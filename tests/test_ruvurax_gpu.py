@@ -299,13 +299,17 @@ def test_recurrent_unit_carries_its_state_across_portions(dtype, bound, plan):
     assert torch.isnan(state[1]).all() and torch.isnan(state[3]).all()      # other slots are never touched
 
 
-@pytest.mark.parametrize("heads,dk,dv", [(2, 12, 36), (1, 64, 32), (3, 9, 5)])
-def test_gated_linear_attention_state(heads, dk, dv):
+@pytest.mark.parametrize("heads,dk,dv,dtype,portions", [
+    (2, 12, 36, torch.float32, (1, 17, 2, 1, 1, 20, 3)), (1, 64, 32, torch.float32, (1, 17, 2, 1, 1, 20, 3)),
+    (3, 9, 5, torch.float32, (1, 17, 2, 1, 1, 20, 3)),
+    (2, 24, 40, torch.bfloat16, (300, 1, 140, 129)), (1, 128, 64, torch.bfloat16, (513,))])   # chunks side by side
+def test_gated_linear_attention_state(heads, dk, dv, dtype, portions):
     """The matrix state through portions and decoded tokens against the plain token loop, with decays
     near 1 and near 0, and a head's output norm and gate."""
-    Tn, tau = 45, 3.0
+    Tn, tau = sum(portions), 3.0
     stride = heads * (2 * dk + dv) + 3
-    packed = rnd(Tn, stride, seed=50)
+    stride += (-stride) % 8
+    packed = rnd(Tn, stride, seed=50).to(dtype)
     z = rnd(Tn, heads * dk, seed=51, scale=3.0)
     zb = rnd(heads * dk, seed=52)
     q, k = packed[:, :heads * dk], packed[:, heads * dk:2 * heads * dk]
@@ -321,7 +325,7 @@ def test_gated_linear_attention_state(heads, dk, dv):
     state[1].zero_()
     dev = packed.to(DEV)
     got, t0 = [], 0
-    for n in (1, 17, 2, 1, 1, 20, 3):
+    for n in portions:
         ctx = ctx_for([n], [1])
         sl = dev[t0:t0 + n]
         o = ops().gla_scan(sl[:, :heads * dk], sl[:, heads * dk:2 * heads * dk],
