@@ -406,17 +406,25 @@ moe_stream_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restri
   float acc0[FEW_ROWS], acc1[FEW_ROWS];
 #pragma unroll
   for (int r = 0; r < FEW_ROWS; ++r) acc0[r] = acc1[r] = 0.f;
-#pragma unroll 4
-  for (int k = lane * 8; k < K; k += 256) {
-    const uint4 wv0 = *reinterpret_cast<const uint4*>(wr0 + k);
-    uint4 wv1 = make_uint4(0u, 0u, 0u, 0u);
-    if (GATED) wv1 = *reinterpret_cast<const uint4*>(wr1 + k);
+  // two pieces of every weight row per turn, all four loads in flight before the first is used
+  for (int k = lane * 8; k < K; k += 512) {
+    const bool two = k + 256 < K;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const uint4 wa0 = *reinterpret_cast<const uint4*>(wr0 + k);
+    const uint4 wb0 = two ? *reinterpret_cast<const uint4*>(wr0 + k + 256) : zero;
+    const uint4 wa1 = GATED ? *reinterpret_cast<const uint4*>(wr1 + k) : zero;
+    const uint4 wb1 = (GATED && two) ? *reinterpret_cast<const uint4*>(wr1 + k + 256) : zero;
 #pragma unroll
     for (int r = 0; r < FEW_ROWS; ++r) {
       if (r < rows) {
-        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(aptr[r] + k));
-        fma8(acc0[r], wv0, xv);
-        if (GATED) fma8(acc1[r], wv1, xv);
+        const uint4 xa = __ldg(reinterpret_cast<const uint4*>(aptr[r] + k));
+        fma8(acc0[r], wa0, xa);
+        if (GATED) fma8(acc1[r], wa1, xa);
+        if (two) {
+          const uint4 xb = __ldg(reinterpret_cast<const uint4*>(aptr[r] + k + 256));
+          fma8(acc0[r], wb0, xb);
+          if (GATED) fma8(acc1[r], wb1, xb);
+        }
       }
     }
   }
