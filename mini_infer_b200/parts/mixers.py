@@ -117,7 +117,7 @@ class GatedWindowAttention(ProjectedMixer):
     def _attend(self, q, heads, cache, ctx):
         """bfloat16 with sizes the tensor-core kernels take and aligned rows: those kernels (scores and
         softmax in fp32, as everywhere); else the CUDA-core kernel."""
-        if (q.dtype == torch.bfloat16 and self._tensor_core_sizes() and heads.is_contiguous()
+        if (q.dtype == torch.bfloat16 and self._tensor_core_sizes() and self.scale > 0 and heads.is_contiguous()
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
             ops.attention(q, q.stride(0), heads, cache, ctx, self.nq, self.nkv, self.d, self.scale, self.window or 0)
         else:
