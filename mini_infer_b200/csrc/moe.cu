@@ -16,9 +16,12 @@
 //
 // glu(g, u) = g' * sigmoid(alpha * g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit).
 //
-// float32 products run on CUDA cores with fp32 accumulation, k ascending; bfloat16 products run on the
-// tensor cores (mma.sync m16n8k16, fp32 accumulation, k ascending).  Either way a row's result does
-// not depend on which other rows share its tile.
+// Three products live here, all with fp32 accumulation, and none lets a row's result depend on which
+// other rows share its tile: float32 on CUDA cores, k ascending (moe_gemm_kernel); bfloat16 tiles of 64
+// rows on the tensor cores (mma.sync m16n8k16, moe_gemm_mma_kernel); bfloat16 tiles of 8 rows that
+// stream an expert's weights, one warp per output column (moe_stream_kernel).  Large bfloat16 steps
+// whose rows are whole 16-byte pieces go to the library's grouped product instead (the caller gathers
+// the rows with mi_moe_gather and passes the experts' row ranges from the plan).
 #include "common.cuh"
 
 MI_DEFINE_ERROR_API()
