@@ -217,6 +217,7 @@ __global__ void rglru_chunk_kernel(const float* __restrict__ gates, int M, int b
   const float sp = decay_scale * mi_softplus(lam[c]);
   if (PASS == 1) {
     float A = 1.f, B = 0.f;
+#pragma unroll 4
     for (int t = t0; t < t1; ++t, g += 2 * bw) {
       const RglruTerms k = rglru_terms(g, bw, vbr, vbi, sp, u, (size_t)(row0 + t), u_stride, c);
       B = fmaf(k.a, B, k.b);
@@ -230,6 +231,7 @@ __global__ void rglru_chunk_kernel(const float* __restrict__ gates, int M, int b
   float S = start[c];
   for (int p = 0; p < ci; ++p) S = fmaf(summ[((size_t)p * 2) * C + c], S, summ[((size_t)p * 2 + 1) * C + c]);
   const float yb = y_bias ? y_bias[c] : 0.f;
+#pragma unroll 4
   for (int t = t0; t < t1; ++t, g += 2 * bw) {
     const RglruTerms k = rglru_terms(g, bw, vbr, vbi, sp, u, (size_t)(row0 + t), u_stride, c);
     S = fmaf(k.a, S, k.b);
