@@ -5,7 +5,7 @@ window) form a group.  A group owns its pages: a pool of page ids with a LIFO fr
 list, one storage tensor ``[layers, 2, pages, kv_heads, page_size, head_dim]`` (the keys of a
 page lie together per head, so attention reads long runs; a group whose values have another
 size than its keys keeps two tensors, ``[layers, pages, kv_heads, page_size, head_dim]`` and
-``[..., value_dim]``) and one block table per request.  A page id means the same row range in every layer of its group
+``[..., value_dim]``; a group with ``value_dim`` 0 keeps keys only) and one block table per request.  A page id means the same row range in every layer of its group
 (the reference's pool works that way for its single group, ``cache/block_pool.py:332-351``;
 its free list is LIFO as well, ``:570,735-757``).  Groups with a window give pages back as
 soon as every position in them has fallen out of every future query's window; the table
@@ -88,7 +88,7 @@ class GroupSpec:
     kv_heads: int
     head_dim: int
     window: int | None
-    value_dim: int | None = None   # size of a value per head where it differs from head_dim
+    value_dim: int | None = None   # size of a value per head where it differs from head_dim (0: keys only)
 
 
 @dataclass
@@ -189,6 +189,11 @@ class CacheManager:
                                      dtype=dtype, device=self.device)
                     self.storage.append(st)
                     self._group_kv.append((st[:, 0], st[:, 1]))
+                elif g.value_dim == 0:      # keys only: whoever reads the layer finds the values in the keys
+                    keys = torch.zeros((len(g.layers), n, g.kv_heads, page_size, g.head_dim),
+                                       dtype=dtype, device=self.device)
+                    self.storage.append(keys)
+                    self._group_kv.append((keys, None))
                 else:
                     keys = torch.zeros((len(g.layers), n, g.kv_heads, page_size, g.head_dim),
                                        dtype=dtype, device=self.device)
@@ -363,7 +368,7 @@ class CacheManager:
         ``[pages, kv_heads, page_size, head_dim]`` (values ``[..., value_dim]`` where the group has one)."""
         gi, li = self.layer_place[cache_layer]
         keys, values = self._group_kv[gi]
-        return gi, keys[li], values[li]
+        return gi, keys[li], (values[li] if values is not None else None)
 
     def layer_state(self, cache_layer: int) -> torch.Tensor | None:
         return self.state_arenas.get(cache_layer)

@@ -7,8 +7,13 @@
 // online softmax in fp32.  Keys and values are fetched through the block table; a
 // query at absolute position p sees keys j with  max(0, p - window + 1) <= j <= p
 // (window = 0: all keys up to p).  Keys and values may have different sizes per head (d for
-// queries and keys, dv for values and the output); any size from 1 to 256 is taken, sizes that are
-// no multiple of 4 element by element.
+// queries and keys, dv for values and the output); keys of any size that fits in shared memory
+// and values up to 512 are taken, sizes that are no multiple of 4 element by element.
+//
+// Three optional extras.  `sinks` [nq]: the softmax's denominator also holds exp(sinks[h]), a
+// score without a key or a value that is not scaled and counts once.  `slopes` [nq]: the scaled
+// score of query i and key j is lowered by slopes[h] * (i - j).  `v_prefix`: there is no value
+// cache; the value of a key is the first dv numbers of the key's own row (dv <= d).
 //
 // Layouts
 //   q    [tokens, q_stride]   head h at columns [h*d, (h+1)*d)
@@ -37,12 +42,13 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ q_start, const int* __restrict__ q_len,
                          const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                          const int* __restrict__ tile_tok0, int nq, int nkv, int d, int dv, float scale,
-                         int window) {
+                         int window, const float* __restrict__ sinks, const float* __restrict__ slopes,
+                         int v_prefix) {
   mi_pdl_enter();   // inputs come from the kernels before this one
   extern __shared__ __align__(16) float smem[];
-  float* Vs = smem;                       // [BK][dvp], dvp = dv rounded up to 4
+  float* Vs = smem;                       // [BK][dvp], dvp = dv rounded up to 4 (nothing with v_prefix)
   const int dvp = (dv + 3) & ~3;
-  float* Qs = Vs + BK * dvp;              // [BQ][d]
+  float* Qs = Vs + (v_prefix ? 0 : BK * dvp);   // [BQ][d]
   float* Ks = Qs + BQ * d;                // [BK][d + 1]
   float* Ss = Ks + BK * (d + 1);          // [BQ][BK]
   int* rowbase = reinterpret_cast<int*>(Ss + BQ * BK);  // [BK] element offset / d of each key row, -1: none
@@ -62,6 +68,9 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   const int j_end = p0 + rows;    // one past the last visible key
   const int j_lo = window > 0 ? max(0, p0 - window + 1) : 0;
   const int dp = d + 1;
+  const float* Vrows = v_prefix ? Ks : Vs;   // where the PV product finds a key's value, and its row pitch
+  const int vpitch = v_prefix ? dp : dvp;
+  const float slope = slopes ? slopes[h] : 0.f;
 
   for (int idx = tid; idx < BQ * d; idx += NTHREADS) {
     const int r = idx / d, k = idx - r * d;
@@ -112,7 +121,9 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         Ks[jj * dp + k] = base >= 0 ? mi_to_float(kcache[(size_t)base * d + mi_swizzled(k, rowswz[jj], swz_mask, EPC)]) : 0.f;
       }
     }
-    if ((dv & 3) == 0) {
+    if (v_prefix) {
+      // the values are the keys' own first columns, already in Ks
+    } else if ((dv & 3) == 0) {
       const int d4 = dv >> 2;
       for (int idx = tid; idx < BK * d4; idx += NTHREADS) {
         const int jj = idx / d4, k4 = (idx - jj * d4) << 2;
@@ -147,7 +158,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     for (int jj = 0; jj < 4; ++jj) {
       const int j = j0 + c + 8 * jj;
       const bool ok = (r < rows) && (j <= prow) && (j >= lo_r);
-      s[jj] = ok ? s[jj] * scale : -INFINITY;
+      s[jj] = ok ? s[jj] * scale - slope * (float)(prow - j) : -INFINITY;
       mx = fmaxf(mx, s[jj]);
     }
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -176,11 +187,20 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     __syncthreads();
     for (int j = 0; j < BK; ++j) {
       const float pj = Ss[r * BK + j];
-      const float* vrow = Vs + j * dvp + c;
+      const float* vrow = Vrows + j * vpitch + c;
 #pragma unroll
       for (int e = 0; e < DMAX / 8; ++e)
         if (e < ne && c + 8 * e < dv) acc[e] = fmaf(pj, vrow[8 * e], acc[e]);
     }
+  }
+  if (sinks && r < rows) {
+    // the sink joins the denominator once, on the scale of the larger of itself and the row's maximum
+    const float sink = sinks[h];
+    const float m_f = fmaxf(m_i, sink);
+    const float keep = (m_i == -INFINITY) ? 0.f : expf(m_i - m_f);
+    l_i = l_i * keep + expf(sink - m_f);
+#pragma unroll
+    for (int e = 0; e < DMAX / 8; ++e) acc[e] *= keep;
   }
   if (r < rows && l_i > 0.f) {
     const float inv = 1.f / l_i;
@@ -196,10 +216,11 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
                   const void* vcache, const int* block_table, int bt_stride, const int* table_rows, int page_size,
                   const int* q_start, const int* q_len, const int* kv_len, const int* tile_req,
                   const int* tile_tok0, int n_tiles, int nq, int nkv, int d, int dv, float scale, int window,
-                  cudaStream_t stream) {
-  const size_t smem = ((size_t)BK * ((dv + 3) & ~3) + (size_t)BQ * d + (size_t)BK * (d + 1) + BQ * BK) * sizeof(float) +
-                      2 * BK * sizeof(int);
+                  const float* sinks, const float* slopes, int v_prefix, cudaStream_t stream) {
+  const size_t smem = ((v_prefix ? 0 : (size_t)BK * ((dv + 3) & ~3)) + (size_t)BQ * d + (size_t)BK * (d + 1) + BQ * BK) *
+                          sizeof(float) + 2 * BK * sizeof(int);
   auto kern = attention_generic_kernel<T, DMAX>;
+  if (smem > 227 * 1024) return MI_REFUSED - 1;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -207,21 +228,25 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
   dim3 grid((unsigned)(n_tiles * nq));
   MI_LAUNCH((kern), grid, NTHREADS, smem, stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)kcache,
                                          (const T*)vcache, block_table, bt_stride, table_rows, page_size, q_start,
-                                         q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, dv, scale, window);
+                                         q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, dv, scale, window, sinks, slopes,
+                                         v_prefix);
   return 0;
 }
 
 extern "C" int mi_attention_generic_tile_tokens() { return BQ; }
 
-extern "C" int mi_attention_generic_kv(const void* q, int q_stride, void* out, int out_stride,
-                                       const void* kcache, const void* vcache, const int* block_table,
-                                       int bt_stride, const int* table_rows, int page_size, const int* q_start,
-                                       const int* q_len, const int* kv_len, const int* tile_req,
-                                       const int* tile_tok0, int n_tiles, int nq, int nkv, int d, int dv,
-                                       float scale, int window, int dtype, cudaStream_t stream) {
+extern "C" int mi_attention_generic_ext(const void* q, int q_stride, void* out, int out_stride,
+                                        const void* kcache, const void* vcache, const int* block_table,
+                                        int bt_stride, const int* table_rows, int page_size, const int* q_start,
+                                        const int* q_len, const int* kv_len, const int* tile_req,
+                                        const int* tile_tok0, int n_tiles, int nq, int nkv, int d, int dv,
+                                        float scale, int window, const float* sinks, const float* slopes,
+                                        int v_prefix, int dtype, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (d <= 0 || d > 256 || dv <= 0 || dv > 256)
-    MI_REFUSE("attention: head sizes %d (keys) and %d (values) must lie in [1, 256]", d, dv);
+  if (d <= 0 || d > 1024 || dv <= 0 || dv > 512)
+    MI_REFUSE("attention: head sizes %d (keys, up to 1024) and %d (values, up to 512) are not taken", d, dv);
+  if (v_prefix && dv > d) MI_REFUSE("attention: values of %d cannot be the first columns of keys of %d", dv, d);
+  if (!v_prefix && !vcache) MI_REFUSE("attention: no value cache");
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0)
     MI_REFUSE("attention: %d query heads cannot share %d key/value heads", nq, nkv);
   if ((long long)n_tiles * nq > 0x7fffffffLL) MI_REFUSE("attention: too many blocks for one launch");
@@ -231,21 +256,35 @@ extern "C" int mi_attention_generic_kv(const void* q, int q_stride, void* out, i
 #define MI_GO(T, DMAX)                                                                              \
   rc = launch<T, DMAX>(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride,        \
                        table_rows, page_size, q_start, q_len, kv_len, tile_req, tile_tok0, n_tiles, nq, nkv, d, dv, \
-                       scale, window, stream)
+                       scale, window, sinks, slopes, v_prefix, stream)
   if (dtype == MI_DTYPE_F32) {
     if (dv <= 64) MI_GO(float, 64);
     else if (dv <= 128) MI_GO(float, 128);
-    else MI_GO(float, 256);
+    else if (dv <= 256) MI_GO(float, 256);
+    else MI_GO(float, 512);
   } else if (dtype == MI_DTYPE_BF16) {
     if (dv <= 64) MI_GO(bf16, 64);
     else if (dv <= 128) MI_GO(bf16, 128);
-    else MI_GO(bf16, 256);
+    else if (dv <= 256) MI_GO(bf16, 256);
+    else MI_GO(bf16, 512);
   } else {
     MI_REFUSE("attention: unknown dtype %d", dtype);
   }
 #undef MI_GO
+  if (rc == MI_REFUSED - 1) MI_REFUSE("attention: keys of %d and values of %d do not fit in shared memory", d, dv);
   if (rc) return rc;
   MI_RETURN_LAUNCH_STATUS();
+}
+
+extern "C" int mi_attention_generic_kv(const void* q, int q_stride, void* out, int out_stride,
+                                       const void* kcache, const void* vcache, const int* block_table,
+                                       int bt_stride, const int* table_rows, int page_size, const int* q_start,
+                                       const int* q_len, const int* kv_len, const int* tile_req,
+                                       const int* tile_tok0, int n_tiles, int nq, int nkv, int d, int dv,
+                                       float scale, int window, int dtype, cudaStream_t stream) {
+  return mi_attention_generic_ext(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride, table_rows,
+                                  page_size, q_start, q_len, kv_len, tile_req, tile_tok0, n_tiles, nq, nkv, d, dv,
+                                  scale, window, nullptr, nullptr, 0, dtype, stream);
 }
 
 // keys and values of one size, a multiple of 16 (what the tensor-core kernels take as well)

@@ -42,6 +42,8 @@ LIBRARIES: dict[str, tuple[list[str], list[str], list[str]]] = {
     "rope_norm": (["rope_norm.cu"], ["common.cuh"], []),
     "recurrent": (["recurrent.cu"], ["common.cuh"], []),
     "moe": (["moe.cu"], ["common.cuh"], []),
+    "stream": (["stream.cu"], ["common.cuh"], []),
+    "qk_prepare": (["qk_prepare.cu"], ["common.cuh"], []),
 }
 
 

@@ -35,6 +35,12 @@
 
 MI_DEFINE_ERROR_API()
 
+// The activation of a gated gate/up epilogue: 1 SiLU, 2 the tanh form of GELU.
+__device__ __forceinline__ float mi_glu_act(float g, int act) {
+  if (act == 2) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.f + expf(-g));
+}
+
 #define TILE_ROWS 128   // rows of W per tile: the MMA's M
 #define TILE_K 64       // k elements per stage: 128 bytes of bf16, one swizzle row
 #define UMMA_K 16
@@ -418,7 +424,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         for (int j = 0; j < 16; ++j) {
           const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
           if (!(row & 1) && n < N && c0 + j < M)
-            y[(size_t)(c0 + j) * ldy + (n >> 1)] = mi_from_float<OutT>((v[j] / (1.f + expf(-v[j]))) * other);
+            y[(size_t)(c0 + j) * ldy + (n >> 1)] = mi_from_float<OutT>(mi_glu_act(v[j], swiglu) * other);
         }
       } else if (n < N) {
 #pragma unroll
@@ -612,8 +618,8 @@ extern "C" int mi_gemm_tma_workspace(int M, int N, int blocks, long long* partia
 }
 
 // x [M, K] bf16 (row stride ldx), w [N, K] bf16 contiguous, y [M, N] (row stride ldy) bf16 or
-// fp32.  With `swiglu` the rows of w alternate gate, up and y is [M, N / 2]:
-// y[m, i] = silu(x w[2i]) * (x w[2i+1]), computed on the fp32 accumulators.  `blocks` is the number of persistent blocks (the number of SMs); `partials` and
+// fp32.  With `swiglu` (1: SiLU, 2: the tanh form of GELU) the rows of w alternate gate, up and y is [M, N / 2]:
+// y[m, i] = act(x w[2i]) * (x w[2i+1]), computed on the fp32 accumulators.  `blocks` is the number of persistent blocks (the number of SMs); `partials` and
 // `counters` (zero before the first call; the kernel leaves them zero) as mi_gemm_tma_workspace
 // says.
 //
@@ -636,6 +642,7 @@ extern "C" int mi_gemm_tma_fused(const void* x, long long ldx, const void* w, vo
       MI_REFUSE("gemm_tma: the residual epilogue needs a gain and room for its statistics, and no gate/up pairs");
     if (residual && !mi_aligned(residual, 4)) MI_REFUSE("gemm_tma: misaligned residual stream");
   }
+  if (swiglu < 0 || swiglu > 2) MI_REFUSE("gemm_tma: unknown gate activation %d", swiglu);
   if (swiglu && (N % 2)) MI_REFUSE("gemm_tma: the gate/up epilogue needs an even number of rows of W, got %d", N);
   if (M <= 0 || N <= 0) return 0;
   if (M > MAX_TOKENS) MI_REFUSE("gemm_tma: %d rows of x; this kernel takes at most %d", M, MAX_TOKENS);
@@ -686,7 +693,7 @@ extern "C" int mi_gemm_tma_fused(const void* x, long long ldx, const void* w, vo
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                        \
     if (e != cudaSuccess) return (int)e;                                                                           \
     MI_LAUNCH((kern), grid, GT_THREADS, smem, stream, map_w, map_x, (T*)y, (int)ldy, M, N, K, n_tok, stages, kb,   \
-              chunked, swiglu ? 1 : 0, partials, counters, fus, w_evict_first);                                                   \
+              chunked, swiglu, partials, counters, fus, w_evict_first);                                                   \
   }
   const bool fused = stats_in || residual;
   const int w_evict_first = mi_l2_hints_enabled() ? 1 : 0;

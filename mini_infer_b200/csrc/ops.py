@@ -148,6 +148,10 @@ def _sig_attention_generic(lib: ctypes.CDLL) -> None:
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
         c_float, c_int, c_int, c_void_p]
+    lib.mi_attention_generic_ext.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+        c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
 
 
 def _sig_sampling(lib: ctypes.CDLL) -> None:
@@ -256,7 +260,28 @@ def _sig_moe(lib: ctypes.CDLL) -> None:
     lib.mi_clamped_glu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]
 
 
+def _sig_stream(lib: ctypes.CDLL) -> None:
+    ll = ctypes.c_longlong
+    lib.mi_embedding_pair_hash.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, ll, ll, c_int,
+                                           c_void_p]
+    lib.mi_add_rmsnorm_multi.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
+    lib.mi_glu_mul_pairs.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+
+
+def _sig_qk_prepare(lib: ctypes.CDLL) -> None:
+    lib.mi_qk_bias_norm_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p,
+                                          c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mi_latent_prepare.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p,
+                                      c_void_p, c_int, c_int, c_int, c_void_p]
+
+
 _SIGNATURES = {
+    "stream": _sig_stream,
+    "qk_prepare": _sig_qk_prepare,
     "layernorm": _sig_layernorm,
     "rope_norm": _sig_rope_norm,
     "recurrent": _sig_recurrent,
@@ -912,13 +937,14 @@ class RowStats:
 
 
 def gemm_tma(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-             swiglu: bool = False, row_stats: RowStats | None = None,
+             swiglu: bool | int = False, row_stats: RowStats | None = None,
              residual: torch.Tensor | None = None, gain: torch.Tensor | None = None,
              eps: float = 0.0):
     """``x [M <= 128, K] @ w [N, K]^T`` for bfloat16 operands on the tcgen05 tensor cores,
     streaming ``w`` once through TMA (gemm_tma.cu); the result is bfloat16 or float32.  With
-    ``swiglu`` the rows of ``w`` alternate gate, up and the result is ``[M, N / 2]``:
-    ``silu(gate) * up`` computed on the fp32 accumulators in the product's epilogue.
+    ``swiglu`` (True or 1: SiLU; 2: the tanh form of GELU) the rows of ``w`` alternate gate, up and
+    the result is ``[M, N / 2]``: ``act(gate) * up`` computed on the fp32 accumulators in the
+    product's epilogue.
 
     Two fused forms for at most 16 rows.  ``row_stats``: every row of the product is first
     scaled by ``rsqrt(sum of its squares / width + eps)`` (the input was multiplied by a norm's
@@ -957,7 +983,7 @@ def gemm_tma(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bf
         stats_out = torch.empty((-(-N // TMA_GEMM_TILE_ROWS), TMA_GEMM_STAT_TOKENS), dtype=torch.float32,
                                 device=x.device)
     rc = lib.mi_gemm_tma_fused(_ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), n_out, M, N, K,
-                               _code(out_dtype), 1 if swiglu else 0, blocks, _ptr(partial), _ptr(count),
+                               _code(out_dtype), int(swiglu), blocks, _ptr(partial), _ptr(count),
                                _ptr(sums_in), tiles_in or 0, width or 0, row_stats.eps if row_stats else 0.0,
                                _ptr(residual), _ptr(gain), _ptr(stats_out), _stream())
     _finish(lib, rc, "gemm_tma")
@@ -995,17 +1021,26 @@ def linear_into_stream(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor,
     return gemm_tma(x, w, torch.bfloat16, residual=residual, gain=gain, eps=eps)
 
 
-def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, row_stats: "RowStats | None" = None) -> torch.Tensor:
-    """``silu(x Wg^T) * (x Wu^T)`` for a merged projection whose rows alternate gate, up
-    (``w_pairs [2 I, K]``).  Decode-sized bfloat16 inputs run the product and the activation
-    as one kernel (gemm_tma with its gate/up epilogue); everything else runs ``linear`` and
-    the SiLU-multiply kernel on the interleaved result.  ``row_stats``: see ``gemm_tma``."""
+GLU_ACT = {"silu": 1, "gelu_tanh": 2}
+
+
+def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, row_stats: "RowStats | None" = None,
+                  act: str = "silu") -> torch.Tensor:
+    """``act(x Wg^T) * (x Wu^T)`` for a merged projection whose rows alternate gate, up
+    (``w_pairs [2 I, K]``); ``act`` is ``"silu"`` or ``"gelu_tanh"``.  Decode-sized bfloat16 inputs
+    run the product and the activation as one kernel (gemm_tma with its gate/up epilogue);
+    everything else runs ``linear`` and an activation-and-multiply kernel on the interleaved
+    result.  ``row_stats``: see ``gemm_tma``."""
+    if act not in GLU_ACT:
+        raise KernelError(f"linear_swiglu: unknown activation {act!r}")
     if (x.dtype == torch.bfloat16 and USE_TMA_GEMM and x.shape[0] <= TMA_GEMM_DISPATCH_ROWS
             and w_pairs.dtype == torch.bfloat16 and gemm_tma_ok(x, w_pairs)):
-        return gemm_tma(x, w_pairs, torch.bfloat16, swiglu=True, row_stats=row_stats)
+        return gemm_tma(x, w_pairs, torch.bfloat16, swiglu=GLU_ACT[act], row_stats=row_stats)
     if row_stats is not None:
         raise KernelError("linear_swiglu: row statistics need the streaming product (ask linear_fusable first)")
-    return silu_mul(linear(x, w_pairs), pairs=True)
+    if act == "silu":
+        return silu_mul(linear(x, w_pairs), pairs=True)
+    return glu_mul_pairs(linear(x, w_pairs), act)
 
 
 _MM_OUT_DTYPE: bool | None = None
@@ -1487,3 +1522,232 @@ def block_diagonal_gates(u: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     launch_count += 1
     ub = u.unflatten(1, (blocks, bw)).transpose(0, 1)           # [blocks, M, bw], a view
     return torch.bmm(ub, w.transpose(1, 2), out_dtype=torch.float32)
+
+
+# --------------------------------------------------------------------------------------- streams with several addends
+
+
+def embedding_pair_hash(table: torch.Tensor, pair_table: torch.Tensor, ctx, last_token: torch.Tensor, buckets: int,
+                        mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """``float(table[id]) + float(pair_table[row])`` as the fp32 residual stream ``[M, H]``, ``row``
+    a hash of the token and the one before it, ``(prev * mul_prev + id * mul_cur) mod buckets``,
+    and row ``buckets`` for a sequence's first token.  ``last_token`` (int32 ``[request slots]``)
+    holds, per request, the last token of its previous portion; the kernel reads it for a
+    portion's first token and replaces it by the portion's last one."""
+    ids = ctx.token_ids
+    _cuda(table, pair_table, ids, last_token)
+    if table.dim() != 2 or not table.is_contiguous() or pair_table.dim() != 2 or not pair_table.is_contiguous():
+        raise KernelError("embedding: tables must be contiguous [rows, H] matrices")
+    V, H = table.shape
+    if pair_table.shape != (buckets + 1, H) or pair_table.dtype != table.dtype:
+        raise KernelError(f"embedding: the pair table must be [{buckets + 1}, {H}] in the token table's dtype")
+    if last_token.dtype != torch.int32 or not last_token.is_contiguous():
+        raise KernelError("embedding: the last-token state must be contiguous int32")
+    M = ids.shape[0]
+    out = torch.empty((M, H), dtype=torch.float32, device=table.device)
+    lib = _lib("stream")
+    rc = lib.mi_embedding_pair_hash(_ptr(table), _ptr(pair_table), _ptr(ids), _ptr(ctx.positions), _ptr(ctx.q_start),
+                                    _ptr(ctx.q_len), _ptr(ctx.state_slot), _ptr(last_token), int(ctx.n_requests),
+                                    _ptr(out), M, H, V, int(buckets), int(mul_prev), int(mul_cur), _code(table.dtype),
+                                    _stream())
+    _finish(lib, rc, "embedding")
+    return out
+
+
+def add_rmsnorm_multi(stream: torch.Tensor | None, adds, gain: torch.Tensor, eps: float, dtype: torch.dtype, *,
+                      add32: torch.Tensor | None = None, row_add: torch.Tensor | None = None,
+                      rows: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
+    """RMS norm of ``r = stream + sum(adds) + add32 + row_add`` in fp32: ``stream`` the fp32 stream
+    ``[M, H]``, ``adds`` up to two ``[M, H]`` tensors of ``dtype`` (branch outputs), ``add32`` an fp32
+    ``[M, H]`` tensor, ``row_add`` an fp32 ``[H]`` vector added to every row; each may be missing.
+    Returns ``(gain * r * rsqrt(mean(r^2) + eps)`` in ``dtype``, the new fp32 stream ``r``)``; with
+    ``rows`` (int32) only those rows are normalised and no stream is returned."""
+    adds = [a for a in adds if a is not None]
+    if len(adds) > 2:
+        raise KernelError("rmsnorm: at most two addends in the compute dtype")
+    _cuda(stream, add32, row_add, rows, gain, *adds)
+    shape = next((tuple(t.shape) for t in (stream, add32, *adds) if t is not None), None)
+    if shape is None or len(shape) != 2:
+        raise KernelError("rmsnorm: nothing to normalise")
+    H = shape[1]
+    for t, dt, what in ((stream, torch.float32, "the stream"), (add32, torch.float32, "the fp32 addend"),
+                        *((a, dtype, "an addend") for a in adds)):
+        if t is not None and (t.dtype != dt or tuple(t.shape) != shape or not t.is_contiguous()):
+            raise KernelError(f"rmsnorm: {what} must be contiguous {dt} {shape}")
+    if gain.dtype != torch.float32 or gain.shape != (H,) or not gain.is_contiguous():
+        raise KernelError(f"rmsnorm: the gain must be fp32 [{H}]")
+    if row_add is not None and (row_add.dtype != torch.float32 or row_add.shape != (H,) or not row_add.is_contiguous()):
+        raise KernelError(f"rmsnorm: the row addend must be fp32 [{H}]")
+    if rows is not None and (rows.dtype != torch.int32 or rows.dim() != 1 or not rows.is_contiguous()):
+        raise KernelError("rmsnorm: rows must be a contiguous int32 vector")
+    M = shape[0] if rows is None else rows.shape[0]
+    out = torch.empty((M, H), dtype=dtype, device=gain.device)
+    new_stream = None if rows is not None else torch.empty((M, H), dtype=torch.float32, device=gain.device)
+    lib = _lib("stream")
+    rc = lib.mi_add_rmsnorm_multi(_ptr(stream), _ptr(adds[0] if adds else None), _ptr(adds[1] if len(adds) > 1 else None),
+                                  _ptr(add32), _ptr(row_add), _ptr(new_stream), _ptr(rows), _ptr(gain), _ptr(out),
+                                  M, H, float(eps), _code(dtype), _stream())
+    _finish(lib, rc, "rmsnorm")
+    return out, new_stream
+
+
+def glu_mul_pairs(gate_up: torch.Tensor, act: str, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``act(gate) * up`` with fp32 arithmetic for ``gate_up [M, 2 I]`` whose columns alternate
+    gate, up; ``act`` is ``"silu"`` or ``"gelu_tanh"``."""
+    _cuda(gate_up, out)
+    if gate_up.dim() != 2 or gate_up.shape[1] % 2 or not gate_up.is_contiguous():
+        raise KernelError("glu_mul: input must be contiguous [M, 2 I]")
+    M, I2 = gate_up.shape
+    I = I2 // 2
+    if out is None:
+        out = torch.empty((M, I), dtype=gate_up.dtype, device=gate_up.device)
+    elif out.shape != (M, I) or out.dtype != gate_up.dtype or not out.is_contiguous():
+        raise KernelError("glu_mul: bad output tensor")
+    lib = _lib("stream")
+    rc = lib.mi_glu_mul_pairs(_ptr(gate_up), _ptr(out), M, I, GLU_ACT[act], _code(gate_up.dtype), _stream())
+    _finish(lib, rc, "glu_mul")
+    return out
+
+
+# --------------------------------------------------------------------------------------- between projection and attention
+
+
+def _opt_f32(t: torch.Tensor | None, n: int, what: str) -> None:
+    if t is not None and (not t.is_cuda or t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+        raise KernelError(f"{what}: needs a contiguous fp32 CUDA tensor of {n} elements")
+
+
+def qk_bias_norm_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int, nq: int, nkv: int, d: int, dv: int, *,
+                       q_bias: torch.Tensor | None, k_bias: torch.Tensor | None, q_gain: torch.Tensor | None,
+                       k_gain: torch.Tensor | None, eps: float, values_are_keys: bool,
+                       slots: torch.Tensor | None = None, kcache: torch.Tensor | None = None,
+                       vcache: torch.Tensor | None = None) -> None:
+    """In the packed projection ``[M, stride]`` (q at columns ``q_off``, ``nq`` heads of ``d``; k at
+    ``k_off``, ``nkv`` heads of ``d``): add the biases (fp32 ``[heads * d]``), then give every head an
+    RMS norm with the gain shared by the heads (fp32 ``[d]``; None: no norm); q and k are written back
+    and k is stored at ``slots`` of ``kcache``.  The values stored in ``vcache`` are the keys with
+    their bias before the norm (``values_are_keys``), or the columns at ``v_off`` (``nkv`` heads of ``dv``)."""
+    _cuda(packed, slots, kcache, vcache)
+    _cols(packed, "qk_prepare")
+    M, width = packed.shape
+    if q_off + nq * d > width or k_off + nkv * d > width or (not values_are_keys and v_off + nkv * dv > width):
+        raise KernelError("qk_prepare: a column range lies outside the packed projection")
+    _opt_f32(q_bias, nq * d, "qk_prepare (q bias)")
+    _opt_f32(k_bias, nkv * d, "qk_prepare (k bias)")
+    _opt_f32(q_gain, d, "qk_prepare (q gain)")
+    _opt_f32(k_gain, d, "qk_prepare (k gain)")
+    writes = kcache is not None
+    page_size = 0
+    if writes:
+        if slots is None or slots.dtype != torch.int32 or slots.shape != (M,):
+            raise KernelError("qk_prepare: slots must be int32 [M]")
+        for c, size in ((kcache, d), (vcache, dv)):
+            if (c is None or c.dtype != packed.dtype or c.dim() != 4 or c.shape[1] != nkv or c.shape[3] != size
+                    or not c.is_contiguous()):
+                raise KernelError("qk_prepare: caches must be contiguous [pages, nkv, page_size, size] in the packed dtype")
+        page_size = int(kcache.shape[2])
+    lib = _lib("qk_prepare")
+    rc = lib.mi_qk_bias_norm_store(_ptr(packed), packed.stride(0), q_off, k_off, v_off, M, nq, nkv, d, dv,
+                                   _ptr(q_bias), _ptr(k_bias), _ptr(q_gain), _ptr(k_gain), float(eps),
+                                   1 if values_are_keys else 0, _ptr(slots), _ptr(kcache), _ptr(vcache), page_size,
+                                   1 if writes else 0, _code(packed.dtype), _stream())
+    _finish(lib, rc, "qk_prepare")
+
+
+def latent_prepare(packed: torch.Tensor, q_off: int, nq: int, q_head: int, q_rot_off: int, c_off: int, rank: int,
+                   rot_dim: int, rot: int, *, positions: torch.Tensor, freq: torch.Tensor, c_gain: torch.Tensor,
+                   eps: float, qfull: torch.Tensor, slots: torch.Tensor | None = None,
+                   kcache: torch.Tensor | None = None) -> None:
+    """From the packed projection ``[M, stride]`` of a latent attention: the latent (``rank`` columns
+    at ``c_off``) gets an RMS norm with ``c_gain``; the key part behind it (``rot_dim`` columns) and
+    every query head's part at ``q_rot_off`` within its ``q_head`` columns are rotated by the
+    position (half layout over the first ``rot`` dimensions, ``freq`` float64 ``[rot / 2]``).  The
+    cache row ``[latent, rotated key part]`` is stored at ``slots`` of ``kcache``
+    ``[pages, 1, page_size, rank + rot_dim]``; the rotated query parts go behind the first ``rank``
+    columns of every head of ``qfull [M, nq, rank + rot_dim]``."""
+    _cuda(packed, positions, freq, c_gain, qfull, slots, kcache)
+    _cols(packed, "latent_prepare")
+    M, width = packed.shape
+    if q_off + nq * q_head > width or c_off + rank + rot_dim > width:
+        raise KernelError("latent_prepare: a column range lies outside the packed projection")
+    if positions.dtype != torch.int32 or positions.shape != (M,):
+        raise KernelError("latent_prepare: positions must be int32 [M]")
+    if rot and (freq.dtype != torch.float64 or freq.shape != (rot // 2,) or not freq.is_contiguous()):
+        raise KernelError("latent_prepare: freq must be float64 [rot / 2]")
+    _opt_f32(c_gain, rank, "latent_prepare (gain)")
+    dk = rank + rot_dim
+    if qfull.shape != (M, nq, dk) or qfull.dtype != packed.dtype or not qfull.is_contiguous():
+        raise KernelError(f"latent_prepare: qfull must be contiguous [{M}, {nq}, {dk}] in the packed dtype")
+    writes = kcache is not None
+    page_size = 0
+    if writes:
+        if slots is None or slots.dtype != torch.int32 or slots.shape != (M,):
+            raise KernelError("latent_prepare: slots must be int32 [M]")
+        if (kcache.dtype != packed.dtype or kcache.dim() != 4 or kcache.shape[1] != 1 or kcache.shape[3] != dk
+                or not kcache.is_contiguous()):
+            raise KernelError(f"latent_prepare: the cache must be contiguous [pages, 1, page_size, {dk}] in the packed dtype")
+        page_size = int(kcache.shape[2])
+    lib = _lib("qk_prepare")
+    rc = lib.mi_latent_prepare(_ptr(packed), packed.stride(0), q_off, M, nq, q_head, q_rot_off, c_off, rank, rot_dim,
+                               int(rot), _ptr(positions), _ptr(freq), _ptr(c_gain), float(eps), _ptr(qfull),
+                               nq * dk, dk, _ptr(slots), _ptr(kcache), page_size, 1 if writes else 0,
+                               _code(packed.dtype), _stream())
+    _finish(lib, rc, "latent_prepare")
+
+
+def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: int, d: int, dv: int, scale: float, *,
+                  window: int = 0, sinks: torch.Tensor | None = None, slopes: torch.Tensor | None = None,
+                  values_in_keys: bool = False) -> None:
+    """``attention_kv`` with the extras of the CUDA-core kernel: ``sinks`` (fp32 ``[nq]``: a score per
+    head that joins the softmax's denominator without a key or a value), ``slopes`` (fp32 ``[nq]``:
+    the scaled score of a key ``dist`` positions back is lowered by ``slope * dist``) and
+    ``values_in_keys`` (the cache layer has keys only; a key's value is the first ``dv`` numbers of its
+    own row).  fp32 scores, weights and sums for float32 and bfloat16 alike."""
+    group = ctx.groups[cache.group]
+    _cuda(q, out, cache.k, None if values_in_keys else cache.v, sinks, slopes)
+    _cols(q, "attention")
+    _cols(out, "attention")
+    if q.shape[1] != nq * d or out.shape[1] != nq * dv or q.dtype != out.dtype:
+        raise KernelError("attention: q must be [M, nq * d] and out [M, nq * dv] in one dtype")
+    _opt_f32(sinks, nq, "attention (sinks)")
+    _opt_f32(slopes, nq, "attention (slopes)")
+    kc, vc = cache.k, (None if values_in_keys else cache.v)
+    if kc.dtype != q.dtype or kc.dim() != 4 or kc.shape[1:] != (nkv, group.page_size, d) or not kc.is_contiguous():
+        raise KernelError("attention: the key cache must be contiguous [pages, nkv, page_size, d] in q's dtype")
+    if vc is not None and (vc.dtype != q.dtype or vc.dim() != 4 or vc.shape[1:] != (nkv, group.page_size, dv)
+                           or not vc.is_contiguous()):
+        raise KernelError("attention: the value cache must be contiguous [pages, nkv, page_size, dv] in q's dtype")
+    tile_req, tile_tok0, n_tiles = ctx.q_tiles(ATTENTION_TILE_TOKENS)
+    lib = _lib("attention_generic")
+    if lib.mi_attention_generic_tile_tokens() != ATTENTION_TILE_TOKENS:
+        raise KernelError("attention: the kernel's tile size differs from ATTENTION_TILE_TOKENS")
+    bt = group.block_table
+    rc = lib.mi_attention_generic_ext(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kc), _ptr(vc), _ptr(bt), bt.stride(0),
+        _ptr(group.table_rows), int(group.page_size), _ptr(ctx.q_start), _ptr(ctx.q_len), _ptr(ctx.kv_len),
+        _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), nq, nkv, d, dv, float(scale), int(window),
+        _ptr(sinks), _ptr(slopes), 1 if values_in_keys else 0, _code(q.dtype), _stream())
+    _finish(lib, rc, "attention")
+
+
+def batched_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """One small product per head: ``out[m, b, :] = w[b] x[m, b, :]`` for ``x [M, B, K]`` and ``out
+    [M, B, N]`` (views with unit inner stride are fine) and ``w [B, N, K]`` contiguous.  float32 runs
+    the true-fp32 kernel head by head; bfloat16 the library's batched product with fp32 accumulation."""
+    global launch_count
+    _cuda(x, w, out)
+    if x.dim() != 3 or out.dim() != 3 or w.dim() != 3 or not w.is_contiguous():
+        raise KernelError("batched_linear: x [M, B, K], w [B, N, K] contiguous, out [M, B, N]")
+    M, B, K = x.shape
+    N = w.shape[1]
+    if w.shape != (B, N, K) or out.shape != (M, B, N) or x.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelError(f"batched_linear: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not match")
+    if x.dtype == torch.float32:
+        for b in range(B):
+            gemm_f32(x[:, b], w[b], out=out[:, b])
+        return out
+    if not (x.dtype == w.dtype == out.dtype == torch.bfloat16):
+        raise KernelError("batched_linear: operands must share float32 or bfloat16")
+    launch_count += 1
+    torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+    return out

@@ -1,0 +1,190 @@
+// Kernels around an fp32 residual stream that takes several addends at once.
+//
+//   mi_embedding_pair_hash   stream[t, :] = float(table[id_t, :]) + float(pair_table[row_t, :])     (fp32 out)
+//                            row_t = (prev_t * mul_prev + id_t * mul_cur) mod buckets, and row `buckets`
+//                            (the table's last row) for a sequence's first token (position 0).  prev_t is
+//                            the token before t: the one before it in the step's portion, or, for a
+//                            portion's first token, the request's entry of last_token[] (per request
+//                            slot), which the block of that first token then replaces by the portion's
+//                            last token.
+//   mi_add_rmsnorm_multi     r = stream_in[src] + (float(add1[src]) + float(add2[src])) + add32[src] + row_add
+//                            (fp32; every addend optional); stream_out[i] = r (if given; may be stream_in
+//                            when there is no gather); out[i] = T(r * rsqrt(mean(r^2) + eps) * gain).
+//                            One block per output row; src = rows[i] when a gather list is given, else i.
+//   mi_glu_mul_pairs         out[m, i] = T(act(gu[m, 2i]) * gu[m, 2i + 1]), act = SiLU (1) or the tanh form
+//                            of GELU (2): the layout of a merged gate/up product whose rows alternate.
+#include "common.cuh"
+
+MI_DEFINE_ERROR_API()
+
+template <typename T>
+__global__ void embedding_pair_hash_kernel(const T* __restrict__ table, const T* __restrict__ pair_table,
+                                           const int* __restrict__ ids, const int* __restrict__ positions,
+                                           const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                           const int* __restrict__ state_slot, int* __restrict__ last_token,
+                                           int n_requests, float* __restrict__ out, int H, int V, int buckets,
+                                           long long mul_prev, long long mul_cur) {
+  mi_pdl_enter();
+  const int t = blockIdx.x;
+  int lo = 0, hi = n_requests - 1;      // the request of token t: the last one whose portion starts at or before t
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (q_start[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  const int first = q_start[lo];
+  const int id = ids[t];
+  const int slot = state_slot[lo];
+  const int prev = t > first ? ids[t - 1] : last_token[slot];
+  __syncthreads();                      // every thread has read the entry before one of them replaces it
+  if (t == first && threadIdx.x == 0) last_token[slot] = ids[first + q_len[lo] - 1];
+  float* dst = out + (size_t)t * H;
+  if ((unsigned)id >= (unsigned)V) {    // the step function validates ids; this keeps a fault visible
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = __int_as_float(0x7fc00000);
+    return;
+  }
+  long long row = buckets;
+  if (positions[t] != 0) {
+    row = ((long long)prev * mul_prev + (long long)id * mul_cur) % (long long)buckets;
+    if (row < 0) row += buckets;
+  }
+  const T* a = table + (size_t)id * H;
+  const T* b = pair_table + (size_t)row * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = mi_to_float(a[i]) + mi_to_float(b[i]);
+}
+
+extern "C" int mi_embedding_pair_hash(const void* table, const void* pair_table, const int* ids, const int* positions,
+                                      const int* q_start, const int* q_len, const int* state_slot, int* last_token,
+                                      int n_requests, float* out, int M, int H, int V, int buckets,
+                                      long long mul_prev, long long mul_cur, int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (H <= 0 || V <= 0 || buckets <= 0 || n_requests <= 0) MI_REFUSE("embedding: bad sizes H=%d V=%d buckets=%d", H, V, buckets);
+  const int threads = H >= 1024 ? 256 : 128;
+  if (dtype == MI_DTYPE_F32)
+    MI_LAUNCH((embedding_pair_hash_kernel<float>), M, threads, 0, stream, (const float*)table, (const float*)pair_table,
+              ids, positions, q_start, q_len, state_slot, last_token, n_requests, out, H, V, buckets, mul_prev, mul_cur);
+  else if (dtype == MI_DTYPE_BF16)
+    MI_LAUNCH((embedding_pair_hash_kernel<bf16>), M, threads, 0, stream, (const bf16*)table, (const bf16*)pair_table,
+              ids, positions, q_start, q_len, state_slot, last_token, n_requests, out, H, V, buckets, mul_prev, mul_cur);
+  else
+    MI_REFUSE("embedding: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+template <typename T>
+__global__ void add_rmsnorm_multi_kernel(const float* __restrict__ stream_in, const T* __restrict__ add1,
+                                         const T* __restrict__ add2, const float* __restrict__ add32,
+                                         const float* __restrict__ row_add, float* __restrict__ stream_out,
+                                         const int* __restrict__ rows, const float* __restrict__ gain,
+                                         T* __restrict__ out, int H, float eps) {
+  mi_pdl_enter();
+  extern __shared__ float smem[];
+  float* red = smem;        // 32 floats
+  float* row = smem + 32;   // H floats
+  const int i = blockIdx.x;
+  const int src = rows ? rows[i] : i;
+  const float* sr = stream_in ? stream_in + (size_t)src * H : nullptr;
+  const T* a1 = add1 ? add1 + (size_t)src * H : nullptr;
+  const T* a2 = add2 ? add2 + (size_t)src * H : nullptr;
+  const float* a3 = add32 ? add32 + (size_t)src * H : nullptr;
+  float sq = 0.f;
+  for (int k = threadIdx.x; k < H; k += blockDim.x) {
+    float branches = 0.f;
+    if (a1) branches = mi_to_float(a1[k]);
+    if (a2) branches += mi_to_float(a2[k]);
+    float r = sr ? sr[k] + branches : branches;
+    if (a3) r += a3[k];
+    if (row_add) r += row_add[k];
+    row[k] = r;
+    sq += r * r;
+  }
+  const float rstd = 1.f / sqrtf(mi_block_sum(sq, red) / (float)H + eps);
+  float* so = stream_out ? stream_out + (size_t)i * H : nullptr;
+  T* o = out + (size_t)i * H;
+  for (int k = threadIdx.x; k < H; k += blockDim.x) {
+    const float r = row[k];
+    if (so) so[k] = r;
+    o[k] = mi_from_float<T>(r * rstd * gain[k]);
+  }
+}
+
+extern "C" int mi_add_rmsnorm_multi(const float* stream_in, const void* add1, const void* add2, const float* add32,
+                                    const float* row_add, float* stream_out, const int* rows, const float* gain,
+                                    void* out, int M, int H, float eps, int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (H <= 0) MI_REFUSE("rmsnorm: bad width %d", H);
+  if (rows && stream_out) MI_REFUSE("rmsnorm: a gathered norm does not write the stream");
+  const size_t smem = (32 + (size_t)H) * sizeof(float);
+  if (smem > 200 * 1024) MI_REFUSE("rmsnorm: a row of %d floats does not fit in shared memory", H);
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define MI_GO(T)                                                                                          \
+  do {                                                                                                    \
+    auto kern = add_rmsnorm_multi_kernel<T>;                                                              \
+    if (smem > 48 * 1024) {                                                                               \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                                \
+    }                                                                                                     \
+    MI_LAUNCH(kern, M, threads, smem, stream, stream_in, (const T*)add1, (const T*)add2, add32, row_add,   \
+              stream_out, rows, gain, (T*)out, H, eps);                                                   \
+  } while (0)
+  if (dtype == MI_DTYPE_F32) MI_GO(float);
+  else if (dtype == MI_DTYPE_BF16) MI_GO(bf16);
+  else MI_REFUSE("rmsnorm: unknown dtype %d", dtype);
+#undef MI_GO
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+__device__ __forceinline__ float glu_act(float g, int act) {
+  if (act == 2) {
+    const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.f + tanhf(inner));
+  }
+  return g / (1.f + expf(-g));
+}
+
+template <typename T>
+__global__ void glu_mul_pairs_kernel(const T* __restrict__ gu, T* __restrict__ out, int M, int I, int act) {
+  mi_pdl_enter();
+  const size_t n = (size_t)M * I;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x)
+    out[idx] = mi_from_float<T>(glu_act(mi_to_float(gu[2 * idx]), act) * mi_to_float(gu[2 * idx + 1]));
+}
+
+// bfloat16, eight outputs per thread: two 16-byte loads, one 16-byte store
+__global__ void glu_mul_pairs8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, size_t n8, int act) {
+  mi_pdl_enter();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n8; idx += (size_t)gridDim.x * blockDim.x) {
+    const uint4* in = reinterpret_cast<const uint4*>(gu) + 2 * idx;
+    const uint4 a = in[0], b = in[1];
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};   // each word: (gate, up) of one output
+    uint32_t r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[2 * j]));
+      const float2 p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[2 * j + 1]));
+      const __nv_bfloat162 o = __floats2bfloat162_rn(glu_act(p0.x, act) * p0.y, glu_act(p1.x, act) * p1.y);
+      r[j] = *reinterpret_cast<const uint32_t*>(&o);
+    }
+    reinterpret_cast<uint4*>(out)[idx] = make_uint4(r[0], r[1], r[2], r[3]);
+  }
+}
+
+extern "C" int mi_glu_mul_pairs(const void* gu, void* out, int M, int I, int act, int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (I <= 0) MI_REFUSE("glu_mul: bad width %d", I);
+  if (act != 1 && act != 2) MI_REFUSE("glu_mul: unknown activation %d", act);
+  const size_t n = (size_t)M * I;
+  if (dtype == MI_DTYPE_BF16 && I % 8 == 0 && mi_aligned(gu, 16) && mi_aligned(out, 16)) {
+    const size_t n8 = n / 8;
+    const int blocks = (int)((n8 + 255) / 256 < 8192 ? (n8 + 255) / 256 : 8192);
+    MI_LAUNCH((glu_mul_pairs8_kernel), blocks, 256, 0, stream, (const bf16*)gu, (bf16*)out, n8, act);
+    MI_RETURN_LAUNCH_STATUS();
+  }
+  const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+  if (dtype == MI_DTYPE_F32)
+    MI_LAUNCH((glu_mul_pairs_kernel<float>), blocks, 256, 0, stream, (const float*)gu, (float*)out, M, I, act);
+  else if (dtype == MI_DTYPE_BF16)
+    MI_LAUNCH((glu_mul_pairs_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gu, (bf16*)out, M, I, act);
+  else
+    MI_REFUSE("glu_mul: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}

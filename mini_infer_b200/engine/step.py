@@ -288,6 +288,9 @@ class StepRunner:
                     lc.group, lc.k, lc.v = self.cache.layer_kv(entry.cache)
                 lc.state = self.cache.layer_state(entry.cache)
                 caches.append(lc)
+            emb_state = self.cache.layer_state(self.model.embedding_state_index)
+            if emb_state is not None:      # an embedding with a per-request state of its own: one more entry
+                caches.append(LayerCache(state=emb_state, writes=True))
             self._layer_caches = caches
         caches = self._layer_caches
         want = view("want_rows") if hp.rows else None

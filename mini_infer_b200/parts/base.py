@@ -52,7 +52,8 @@ class ParamDecl:
 class KVNeed:
     """Per-token keys and values kept in pages: ``kv_heads * head_dim`` numbers each per
     token.  ``window``: only the last ``window`` positions are ever read (None: all).
-    ``value_dim``: size of a value per head where it is not ``head_dim`` (keys keep ``head_dim``)."""
+    ``value_dim``: size of a value per head where it is not ``head_dim`` (keys keep ``head_dim``);
+    0: nothing is kept beside the keys (the mixer finds its values in them)."""
 
     kv_heads: int
     head_dim: int
@@ -256,11 +257,24 @@ class BranchSum(tuple):
     """Outputs of several branches that read the same stream and whose sum is still to be added to
     it: what a layer with parallel branches hands on in the place of a single ``x``.  A norm that
     knows it adds the parts to the fp32 stream one by one (no rounded sum in between); any other
-    part may ask for ``total()``."""
+    part may ask for ``total()``.
+
+    Two more addends may ride along, both fp32 and never rounded: ``stream_add`` (``[tokens, hidden]``)
+    and ``row_add`` (``[hidden]``, added to every token's row); a stream part puts them there."""
+
+    stream_add: torch.Tensor | None = None
+    row_add: torch.Tensor | None = None
 
     def total(self) -> torch.Tensor:
-        out = self[0]
-        for t in self[1:]:
+        terms = list(self)
+        if self.stream_add is not None:
+            terms.append(self.stream_add)
+        if self.row_add is not None:
+            terms.append(self.row_add)
+        if not terms:
+            raise ValueError("an empty sum of branches")
+        out = terms[0]
+        for t in terms[1:]:
             out = out + t
         return out
 
@@ -324,6 +338,20 @@ class FeedForward(Part):
         return False
 
 
+class StreamPart(Part):
+    """Something a model does to the residual stream between two layers (``ScheduleEntry.before``).
+
+    ``forward(x, residual, ctx, embedded) -> (x, residual)`` with ``(x, residual)`` as layers hand them
+    on (``x``: what is not yet added to the fp32 stream ``residual``; ``residual`` None before the first
+    layer, when ``x`` is the embedding's output) and ``embedded`` the embedding's output of this step,
+    which must not be changed.  ``needs_embedding`` tells the model to keep it."""
+
+    needs_embedding: ClassVar[bool] = False
+
+    def forward(self, x, residual, ctx: StepContext, embedded: torch.Tensor | None):
+        raise NotImplementedError
+
+
 class Arrangement:
     """A layer: a mixer and a feed-forward behind their norms.
 
@@ -369,6 +397,7 @@ _REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {
     "arrangement": {},
     "embedding": {},
     "head": {},
+    "stream": {},
 }
 
 
@@ -407,8 +436,12 @@ def register_head(kind: str, cls, *, replace: bool = False) -> None:
     _register("head", kind, cls, replace)
 
 
+def register_stream_part(kind: str, cls, *, replace: bool = False) -> None:
+    _register("stream", kind, cls, replace)
+
+
 def lookup(family: str, kind: str):
-    from . import builtin, experts, mixers  # noqa: F401  (register the parts that ship with the package)
+    from . import builtin, experts, latent, mixers  # noqa: F401  (register the parts that ship with the package)
 
     try:
         return _REGISTRIES[family][kind]

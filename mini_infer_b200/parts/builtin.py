@@ -93,6 +93,8 @@ class RMSNorm(Norm):
         # a gain stored in 32-bit stays 32-bit; anything else follows the compute dtype
         self.weight = w if w.dtype == torch.float32 else w.to(dtype)
         self.eps = float(self.param("eps"))
+        self.dtype = dtype
+        self._gain32 = None
 
     def stream_sink(self, residual, n_rows):
         if (not ops.fused_norms_enabled() or residual is None
@@ -107,14 +109,38 @@ class RMSNorm(Norm):
             if x.norm is not self or rows is not None:
                 raise ValueError("a deferred norm was handed to another norm than the one it was made for")
             return x, x.residual
-        if isinstance(x, BranchSum):
-            x = x.total()
+        if isinstance(x, BranchSum) or (residual is None and x.dtype == torch.float32 and self.dtype != torch.float32):
+            return self._forward_sum(x, residual, rows)
         if rows is not None:
             return ops.add_rmsnorm(x, self.weight, self.eps, residual_in=residual, rows=rows), None
         new_residual = torch.empty(x.shape, dtype=torch.float32, device=x.device)
         out = ops.add_rmsnorm(x, self.weight, self.eps, residual_in=residual,
                               residual_out=new_residual)
         return out, new_residual
+
+    def _forward_sum(self, x, residual, rows):
+        """Several addends at once, none of them rounded on the way: the outputs of parallel
+        branches (compute dtype), an fp32 tensor and an fp32 row that a stream part left
+        (``BranchSum.stream_add``, ``row_add``); before the first layer an fp32 ``x`` is the stream
+        itself.  The stream that comes in is left as it is; a new one is returned."""
+        if getattr(self, "_gain32", None) is None:
+            self._gain32 = self.weight.to(torch.float32).contiguous()
+        adds, add32, row_add = (), None, None
+        if isinstance(x, BranchSum):
+            adds, add32, row_add = tuple(x), x.stream_add, x.row_add
+        elif residual is None and x.dtype == torch.float32:
+            residual = x
+        else:
+            adds = (x,)
+        return ops.add_rmsnorm_multi(residual, adds, self._gain32, self.eps, self.dtype, add32=add32,
+                                     row_add=row_add, rows=rows)
+
+
+class SameNorm(Norm):
+    """The place of a feed-forward's norm in a layer whose two branches read one norm's output."""
+
+    def forward(self, x, residual, rows=None):
+        raise RuntimeError("this layer's feed-forward reads the mixer's norm")
 
 
 class LayerNorm(Norm):
@@ -354,9 +380,16 @@ class SwiGLU(FeedForward):
     product's epilogue, where both halves of a pair sit side by side; SiLU and the product
     are fp32 per element.
 
-    params: ``hidden_size``, ``intermediate_size``.
+    params: ``hidden_size``, ``intermediate_size``, optional ``activation`` (``"silu"``, the default,
+    or ``"gelu_tanh"``: ``0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))`` in the SiLU's place).
     tensors: ``gate_proj.weight``, ``up_proj.weight``, ``down_proj.weight``.
     """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.activation = str(self.spec.params.get("activation", "silu"))
+        if self.activation not in ops.GLU_ACT:
+            raise ValueError(f"unknown activation {self.activation!r}; known: {sorted(ops.GLU_ACT)}")
 
     def param_decls(self):
         H, I = int(self.param("hidden_size")), int(self.param("intermediate_size"))
@@ -382,9 +415,9 @@ class SwiGLU(FeedForward):
         if isinstance(x, DeferredNorm):
             if x.kind != "rms":
                 raise ValueError(f"this product cannot finish a norm of kind {x.kind!r}")
-            h = ops.linear_swiglu(x.x, self.gate_up_proj.weight, row_stats=x.stats)
+            h = ops.linear_swiglu(x.x, self.gate_up_proj.weight, row_stats=x.stats, act=self.activation)
         else:
-            h = ops.linear_swiglu(x, self.gate_up_proj.weight)
+            h = ops.linear_swiglu(x, self.gate_up_proj.weight, act=self.activation)
         return self.down_proj(h) if into is None else self.down_proj.into_stream(h, into)
 
 
@@ -487,7 +520,9 @@ class ParallelBlock(Arrangement):
     receives the previous layer's branch outputs (a ``BranchSum``, or the embedding before the first
     layer) with the fp32 stream that does not yet include them, adds them while it normalises, and
     returns its own branch outputs unadded.  Two ``LayerNorm``s of one ``eps`` run as one kernel.
-    A layer without a feed-forward (``no_feed_forward``) has the mixer's branch alone."""
+    A layer without a feed-forward (``no_feed_forward``) has the mixer's branch alone; with
+    ``same_norm`` in the feed-forward norm's place both branches read the mixer norm's output
+    (``h += mixer(n) + ffn(n)``, ``n = norm1(h)``)."""
 
     def forward(self, x, residual, ctx, cache):
         ff = None if isinstance(self.feed_forward, NoFeedForward) else self.feed_forward
@@ -495,6 +530,10 @@ class ParallelBlock(Arrangement):
         if ff is None:
             a, stream = n1.forward(x, residual)
             return self.mixer.forward(a, ctx, cache, self.position), stream
+        if isinstance(n2, SameNorm):             # one norm, read by both branches
+            a, stream = n1.forward(x, residual)
+            m = self.mixer.forward(a, ctx, cache, self.position)
+            return BranchSum((m, ff.forward(a, ctx))), stream
         if isinstance(n1, LayerNorm) and isinstance(n2, LayerNorm) and n1.eps == n2.eps:
             a, b, stream = n1.forward_with(n2, x, residual)
         else:
@@ -516,12 +555,14 @@ class NoFeedForward(FeedForward):
 register_norm("rmsnorm", RMSNorm, replace=True)
 register_norm("layernorm", LayerNorm, replace=True)
 register_norm("no_norm", NoNorm, replace=True)
+register_norm("same_norm", SameNorm, replace=True)
 register_position("rotary_interleaved", InterleavedRotary, replace=True)
 register_feed_forward("no_feed_forward", NoFeedForward, replace=True)
 register_arrangement("parallel", ParallelBlock, replace=True)
 register_position("rotary", RotaryPosition, replace=True)
 register_mixer("gqa_attention", GroupedQueryAttention, replace=True)
 register_feed_forward("swiglu", SwiGLU, replace=True)
+register_feed_forward("gated_mlp", SwiGLU, replace=True)
 register_embedding("token_embedding", TokenEmbedding, replace=True)
 register_head("linear_head", OutputHead, replace=True)
 register_arrangement("prenorm", PreNormBlock, replace=True)

@@ -61,6 +61,10 @@ class DecoderModel:
             )
             self.blocks.append(block)
         self.schedule = spec.schedule
+        # stream parts that run before a schedule entry (None where an entry has none)
+        self.before: list[Part | None] = [build_part("stream", e.before) if e.before is not None else None
+                                          for e in spec.schedule]
+        self._keeps_embedding = any(getattr(p, "needs_embedding", False) for p in self.before if p is not None)
         self._bound = False
 
     # ------------------------------------------------------------------ declarations
@@ -69,6 +73,7 @@ class DecoderModel:
         parts: list[Part] = [self.embedding]
         for b in self.blocks:
             parts.extend(b.parts())
+        parts.extend(p for p in self.before if p is not None)
         parts.extend([self.final_norm, self.head])
         return parts
 
@@ -113,7 +118,17 @@ class DecoderModel:
                         f"layer {e.layer} reads cache layer {e.cache} whose key/value shape "
                         f"{owner} does not fit its own {kv}"
                     )
-        return [needs[i] for i in range(self.spec.num_cache_layers)]
+        out = [needs[i] for i in range(self.spec.num_cache_layers)]
+        # an embedding that keeps something per request gets a state arena behind the cache layers'
+        emb_state = getattr(self.embedding, "state_need", lambda: None)()
+        if emb_state is not None:
+            out.append(CacheLayerNeed(self.embedding_state_index, None, emb_state))
+        return out
+
+    @property
+    def embedding_state_index(self) -> int:
+        """The index under which the cache manager keeps the embedding's per-request state."""
+        return self.spec.num_cache_layers
 
     def plan_needs(self) -> PlanNeeds:
         tiles: set[int] = set()
@@ -138,6 +153,9 @@ class DecoderModel:
         for b in self.blocks:
             for part in b.parts():
                 part.bind(local_view(part), dtype, device)
+        for part in self.before:
+            if part is not None:
+                part.bind(local_view(part), dtype, device)
         self.final_norm.bind(local_view(self.final_norm), dtype, device)
         if getattr(self.head, "tied", False):
             self.head.bind({}, dtype, device, tied_weight=self.embedding.weight)
@@ -153,9 +171,15 @@ class DecoderModel:
         """fp32 logits ``[n_want, vocab]`` at the packed rows ``want_rows`` (int32)."""
         if not self._bound:
             raise RuntimeError("the model has no weights yet")
-        x = self.embedding.forward(ctx)
+        if len(caches) > len(self.schedule):     # the embedding's own per-request state
+            x = self.embedding.forward(ctx, caches[len(self.schedule)])
+        else:
+            x = self.embedding.forward(ctx)
+        embedded = x if self._keeps_embedding else None
         residual = None
         for i, (entry, cache) in enumerate(zip(self.schedule, caches)):
+            if self.before[i] is not None:
+                x, residual = self.before[i].forward(x, residual, ctx, embedded)
             block = self.blocks[entry.layer]
             if block.entry() is None:
                 x, residual = block.forward(x, residual, ctx, cache)
