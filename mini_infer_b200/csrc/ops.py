@@ -465,8 +465,9 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
 
 def cache_swizzle_mask(head_dim: int, dtype: torch.dtype) -> int:
     """The chunk permutation mask of cache rows (``mi_swizzle_mask`` in common.cuh)."""
-    n = head_dim * torch.empty((), dtype=dtype).element_size() // 16
-    if n < 2 or n & (n - 1):
+    row_bytes = head_dim * torch.empty((), dtype=dtype).element_size()
+    n = row_bytes // 16
+    if row_bytes % 16 or n < 2 or n & (n - 1):      # a row that is no whole number of chunks is stored as it is
         return 0
     return min(n, 8) - 1
 
