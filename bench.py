@@ -319,6 +319,97 @@ def design_matmul_params(s: dict, layers: int, batch_tokens: int | None) -> floa
     return n_unit * (unit + mlp) + (layers - n_unit) * (left + right + mlp) + s["vocab"] * H
 
 
+# The Lilulix architecture at the same widths: layers alternate attention in a latent space and
+# distance-bias attention, each beside a dense gated feed-forward; the two middle layers run twice.
+LILULIX_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, rot_dim=64, vdim=128, kv_rank=512, ff=5632, vocab=32000),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, rot_dim=64, vdim=128, kv_rank=512, ff=11008, vocab=32000),
+}
+
+
+def lilulix_design(s: dict, layers: int) -> tuple[dict, dict, list[int]]:
+    """(Lilulix configuration, Llama configuration with as many layers as the Lilulix model has layer
+    runs and the same width, heads and feed-forward, the layer of every run)."""
+    mlp = {"kind": "dense", "ff": s["ff"]}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot_dim"], "vdim": s["vdim"],
+                     "kv_rank": s["kv_rank"], "rot": {"base": 10000.0, "dims": s["rot_dim"]},
+                     "scale": (s["dim"] + s["rot_dim"]) ** -0.5}}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                     "scale": s["dim"] ** -0.5}}
+    start, stop = (1, min(3, layers)) if layers >= 2 else (0, 1)
+    raw = {"architecture": "Lilulix", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+           "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+           "layers": [lat if i % 2 == 0 else att for i in range(layers)],
+           "loop": {"start": start, "stop": stop, "times": 2}}
+    runs = list(range(start)) + 2 * list(range(start, stop)) + list(range(stop, layers))
+    llama = dict(LLAMA_8B, hidden_size=s["width"], num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"],
+                 head_dim=s["dim"], intermediate_size=s["ff"], vocab_size=s["vocab"], num_hidden_layers=len(runs))
+    return raw, llama, runs
+
+
+def lilulix_numbers(s: dict, runs: list[int], batch: int, context: float, tokens: int) -> tuple[float, float]:
+    """(bytes a decode step must read, floating-point operations of a prefill of ``tokens``): weights of
+    every layer run, the cache rows of every run's own cache, and the operations of the formulas as
+    written (keys and values expanded from the latent once per token)."""
+    H, n, d, rd, dv, R, nkv, ff = (s[k] for k in ("width", "heads", "dim", "rot_dim", "vdim", "kv_rank", "kv_heads", "ff"))
+    lat_w = H * n * (d + rd) + H * (R + rd) + n * d * R + n * dv * R + 2 * H * n * dv
+    att_w = H * n * d + H * nkv * d + n * d * H
+    mlp_w = 3 * H * ff
+    params = sum((lat_w if i % 2 == 0 else att_w) + mlp_w for i in runs)
+    cache = sum(batch * context * ((R + rd) if i % 2 == 0 else 2 * nkv * d) for i in runs)
+    nbytes = 2.0 * (params + s["vocab"] * H) + 2.0 * cache
+    attention = sum(tokens * tokens * n * ((d + rd + dv) if i % 2 == 0 else 2 * d) for i in runs)   # causal half of 2 T^2 n (dk + dv)
+    flops = 2.0 * tokens * params + 2.0 * s["vocab"] * H + attention
+    return nbytes, flops
+
+
+def run_lilulix_designs(args) -> int:
+    import torch
+
+    from mini_infer_b200.engine import ModelRunner
+
+    peaks = load_peaks()
+    warmup = max(3, args.warmup)
+    out = {"scenario": "designs", "design": "lilulix", "dtype": "bf16", "data": "synthetic", "batch": args.batch,
+           "context": args.context, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks, "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name in args.design_sizes.split(","):
+        s = LILULIX_SIZES[name]
+        layers = args.layers or 4
+        raw_l, raw_llama, runs = lilulix_design(s, layers)
+        cap = args.batch * (args.context + args.steps + warmup + 64) + 2 * PREFILL_TOKENS
+        row = {"layers": layers, "layer_runs": len(runs)}
+        for label, raw in (("lilulix", raw_l), ("llama", raw_llama)):
+            runner = ModelRunner.from_random(raw, seed=0, gain_std=0.0, device="cuda:0", dtype="bfloat16",
+                                             num_blocks=cap // PAGE + 8, block_size=PAGE, max_requests=args.batch,
+                                             cuda_graph=True)
+            ms, launches = time_decode(runner, args.batch, args.context, args.steps, warmup)
+            pms = time_prefill(runner, PREFILL_TOKENS, repeats=3, warmup=2)
+            mid = args.context + warmup + args.steps / 2.0
+            if label == "llama":
+                flops = prefill_flops(raw, len(runs), PREFILL_TOKENS)
+                nbytes = decode_bytes(raw, len(runs), args.batch, mid)
+            else:
+                nbytes, flops = lilulix_numbers(s, runs, args.batch, mid, PREFILL_TOKENS)
+            row[label] = {
+                "decode_tok_s": round(args.batch * 1000.0 / ms, 1), "decode_ms": round(ms, 4),
+                "decode_gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
+                "decode_frac_of_hbm": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pms, 1), "prefill_ms": round(pms, 3),
+                "prefill_frac_of_bf16": round(flops / (pms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+                "launches_per_decode_step": launches // max(1, args.steps),
+            }
+            del runner
+            torch.cuda.empty_cache()
+        out["sizes"][name] = row
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def run_designs(args) -> int:
     import torch
 
@@ -802,8 +893,10 @@ def main() -> int:
                     help="decode: the contract line; long-mixed: many requests of very different lengths "
                          "through the scheduler (a line of its own); serving: the reference's published "
                          "workload, 1024 tokens in and 128 out, single requests and 16 together (a line of its own); "
-                         "designs: the Ruvurax architecture beside Llama at equal sizes, prefill and decode "
+                         "designs: the Ruvurax (or, with --design lilulix, the Lilulix) architecture beside Llama at equal sizes, prefill and decode "
                          "(a line of its own)")
+    ap.add_argument("--design", default="ruvurax", choices=["ruvurax", "lilulix"],
+                    help="designs: which architecture stands beside Llama")
     ap.add_argument("--design-sizes", default="2k,4k", help="designs: which of the sizes " + ",".join(DESIGN_SIZES))
     ap.add_argument("--requests", type=int, default=64, help="long-mixed: requests started together")
     ap.add_argument("--max-prompt", type=int, default=32768, help="long-mixed: longest prompt")
@@ -832,7 +925,7 @@ def main() -> int:
         return run_long_mixed(args)
     if args.scenario == "designs":
         args.layers = None if args.layers == default_layers else args.layers
-        return run_designs(args)
+        return run_lilulix_designs(args) if args.design == "lilulix" else run_designs(args)
     warmup = max(3, args.warmup)
 
     import torch

@@ -288,7 +288,8 @@ class StepRunner:
                     lc.group, lc.k, lc.v = self.cache.layer_kv(entry.cache)
                 lc.state = self.cache.layer_state(entry.cache)
                 caches.append(lc)
-            emb_state = self.cache.layer_state(self.model.embedding_state_index)
+            emb_index = getattr(self.model, "embedding_state_index", None)
+            emb_state = self.cache.layer_state(emb_index) if emb_index is not None else None
             if emb_state is not None:      # an embedding with a per-request state of its own: one more entry
                 caches.append(LayerCache(state=emb_state, writes=True))
             self._layer_caches = caches
