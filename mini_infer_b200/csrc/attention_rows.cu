@@ -1,0 +1,329 @@
+// bfloat16 attention over the paged cache on tensor cores (mma.sync m16n8k16, fp32 accumulation)
+// for the forms the other tensor-core kernels do not take: keys and values of different sizes, keys
+// of any multiple of 16 up to 1024 (a latent row), values that are the first columns of the keys'
+// own rows, a sink score per head in the softmax's denominator, and a distance bias with a slope per
+// head.  Prompt portions and single decoded tokens alike.
+//
+// A block of four warps takes 16 query rows that share one key/value head: with G = nq / nkv query
+// heads per key/value head, the rows are (token, head in group) pairs, 16 / G tokens by G heads when
+// G divides 16, or 16 of the G heads of one token when 16 divides G.  It walks the request's keys in
+// chunks of 64 (cut at absolute multiples of 64): the chunk's rows are gathered from their pages into
+// shared memory (un-permuted), warp w computes the scores of keys 16 w .. 16 w + 15 for all 16 rows
+// (S = Q K^T), the warps exchange row maxima and sums and the bf16 weights through shared memory,
+// and each warp then adds P V for its quarter of the value columns to accumulators in registers.
+// Scores, the softmax and all sums are fp32; the weights are rounded to bf16 for the second product.
+//
+// Layouts as in attention_generic.cu: q [tokens, q_stride], out [tokens, out_stride], kcache
+// [pages, nkv, page_size, d], vcache [pages, nkv, page_size, dv] (null with v_prefix), block tables
+// and the per-request lists of a step; tile_req / tile_tok0 list tiles of `tile_tokens` tokens.
+#include "common.cuh"
+
+MI_DEFINE_ERROR_API()
+
+#define ROWS 16
+#define CHUNK 64
+#define NWARPS 4
+#define PAD 8   // bf16 elements behind every shared-memory row: rows stay 16-byte aligned, banks spread
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// two 8x8 matrices, transposed: lanes 0..7 give the row addresses of the first, 8..15 of the second
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(s));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// DVW: value columns per warp that the accumulators have room for (dv <= 4 * DVW).
+template <int DVW>
+__global__ void __launch_bounds__(NWARPS * 32)
+attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                      const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                      const int* __restrict__ block_table, int bt_stride, const int* __restrict__ table_rows,
+                      int page_size, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                      const int* __restrict__ kv_len, const int* __restrict__ tile_req,
+                      const int* __restrict__ tile_tok0, int tile_tokens, int nq, int nkv, int d, int dv, float scale,
+                      const float* __restrict__ sinks, const float* __restrict__ slopes, int v_prefix) {
+  mi_pdl_enter();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int dp = d + PAD, dvp = dv + PAD;
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [ROWS][dp]
+  bf16* Ks = Qs + ROWS * dp;                                    // [CHUNK][dp]
+  bf16* Vs = Ks + CHUNK * dp;                                   // [CHUNK][dvp] (nothing with v_prefix)
+  bf16* Ps = v_prefix ? Vs : Vs + CHUNK * dvp;                  // [ROWS][CHUNK + PAD]
+  float* wmax = reinterpret_cast<float*>(Ps + ROWS * (CHUNK + PAD));   // [NWARPS][ROWS]
+  float* wsum = wmax + NWARPS * ROWS;                           // [NWARPS][ROWS]
+  int* rowbase = reinterpret_cast<int*>(wsum + NWARPS * ROWS);  // [CHUNK] cache row of each key, -1: none
+  int* rowoff = rowbase + CHUNK;                                // [CHUNK] in-page offset of each key
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;                      // the fragment's row (and row + 8) and column pair
+  const int G = nq / nkv;
+  const int head_tiles = G >= ROWS ? G / ROWS : 1;
+  int bid = blockIdx.x;
+  const int hs = bid % head_tiles;
+  bid /= head_tiles;
+  const int kvh = bid % nkv;
+  const int tile = bid / nkv;
+  const int b = tile_req[tile], tok0 = tile_tok0[tile];
+  const int ql = q_len[b], kl = kv_len[b], qs = q_start[b];
+  const int trow = table_rows ? table_rows[b] : b;
+  const int nt = min(tile_tokens, ql - tok0);                   // tokens of this tile
+  const int p0 = kl - ql + tok0;                                // position of the tile's first token
+  const int j_end = p0 + nt;                                    // one past the last key any row sees
+
+  // a row's token (within the tile) and head
+  auto row_token = [&](int r) { return G >= ROWS ? 0 : r / G; };
+  auto row_head = [&](int r) { return G >= ROWS ? kvh * G + hs * ROWS + r : kvh * G + r % G; };
+
+  // ---- the queries: 16-byte pieces, zero for rows without a token
+  const int pieces = d >> 3;
+  for (int idx = tid; idx < ROWS * pieces; idx += NWARPS * 32) {
+    const int r = idx / pieces, c = idx - r * pieces;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row_token(r) < nt)
+      v = *reinterpret_cast<const uint4*>(q + (size_t)(qs + tok0 + row_token(r)) * q_stride + row_head(r) * d + c * 8);
+    *reinterpret_cast<uint4*>(Qs + r * dp + c * 8) = v;
+  }
+
+  // per thread: the two rows of its fragments
+  const int r_lo = g, r_hi = g + 8;
+  const bool ok_lo = row_token(r_lo) < nt, ok_hi = row_token(r_hi) < nt;
+  const int pos_lo = p0 + row_token(r_lo), pos_hi = p0 + row_token(r_hi);
+  const float slope_lo = slopes ? slopes[row_head(r_lo)] : 0.f, slope_hi = slopes ? slopes[row_head(r_hi)] : 0.f;
+  constexpr float LOG2E = 1.4426950408889634f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;     // running maximum (in units of log2) and sum
+  float acc[DVW / 8][4];
+#pragma unroll
+  for (int n = 0; n < DVW / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+  const int col0 = warp * (dv / NWARPS);                        // this warp's value columns
+  const int ntiles_v = (dv / NWARPS) >> 3;
+  const int mk = mi_swizzle_mask_rows(d, 2), mv = mi_swizzle_mask_rows(dv, 2);
+  const bf16* Vrows = v_prefix ? Ks : Vs;
+  const int vpitch = v_prefix ? dp : dvp;
+
+  for (int j0 = 0; j0 < j_end; j0 += CHUNK) {
+    __syncthreads();                                            // the chunk before is consumed (first time: Qs written)
+    if (tid < CHUNK) {
+      const int j = j0 + tid;
+      int base = -1;
+      if (j < j_end) {
+        const int page = block_table[(size_t)trow * bt_stride + j / page_size];
+        base = (page * nkv + kvh) * page_size + j % page_size;
+      }
+      rowbase[tid] = base;
+      rowoff[tid] = j % page_size;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < CHUNK * pieces; idx += NWARPS * 32) {
+      const int jj = idx / pieces, c = idx - jj * pieces;
+      const int base = rowbase[jj];
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (base >= 0) v = *reinterpret_cast<const uint4*>(kcache + (size_t)base * d + ((c ^ (rowoff[jj] & mk)) << 3));
+      *reinterpret_cast<uint4*>(Ks + jj * dp + c * 8) = v;
+    }
+    if (!v_prefix) {
+      const int vpieces = dv >> 3;
+      for (int idx = tid; idx < CHUNK * vpieces; idx += NWARPS * 32) {
+        const int jj = idx / vpieces, c = idx - jj * vpieces;
+        const int base = rowbase[jj];
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (base >= 0) v = *reinterpret_cast<const uint4*>(vcache + (size_t)base * dv + ((c ^ (rowoff[jj] & mv)) << 3));
+        *reinterpret_cast<uint4*>(Vs + jj * dvp + c * 8) = v;
+      }
+    }
+    __syncthreads();
+
+    // ---- S = Q K^T for this warp's 16 keys: two tiles of 8 keys
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const bf16* qa = Qs + r_lo * dp + 2 * t4;
+    const bf16* kb0 = Ks + (warp * 16 + g) * dp + 2 * t4;
+    const bf16* kb1 = kb0 + 8 * dp;
+    for (int k0 = 0; k0 < d; k0 += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(qa + k0);
+      a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * dp + k0);
+      a[2] = *reinterpret_cast<const uint32_t*>(qa + k0 + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * dp + k0 + 8);
+      mma_bf16(s[0], a, *reinterpret_cast<const uint32_t*>(kb0 + k0), *reinterpret_cast<const uint32_t*>(kb0 + k0 + 8));
+      mma_bf16(s[1], a, *reinterpret_cast<const uint32_t*>(kb1 + k0), *reinterpret_cast<const uint32_t*>(kb1 + k0 + 8));
+    }
+    // ---- scale, distance bias, mask; everything in units of log2
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + warp * 16 + n * 8 + 2 * t4 + (e & 1);
+        const bool hi = e >= 2;
+        const int pos = hi ? pos_hi : pos_lo;
+        const bool ok = (hi ? ok_hi : ok_lo) && j <= pos;
+        const float v = ok ? (s[n][e] * scale - (hi ? slope_hi : slope_lo) * (float)(pos - j)) * LOG2E : -INFINITY;
+        s[n][e] = v;
+        if (hi) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
+      }
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    if (t4 == 0) {
+      wmax[warp * ROWS + r_lo] = mx_lo;
+      wmax[warp * ROWS + r_hi] = mx_hi;
+    }
+    __syncthreads();
+    float cm_lo = wmax[r_lo], cm_hi = wmax[r_hi];
+#pragma unroll
+    for (int w = 1; w < NWARPS; ++w) {
+      cm_lo = fmaxf(cm_lo, wmax[w * ROWS + r_lo]);
+      cm_hi = fmaxf(cm_hi, wmax[w * ROWS + r_hi]);
+    }
+    const float mn_lo = fmaxf(m_lo, cm_lo), mn_hi = fmaxf(m_hi, cm_hi);
+    const float al_lo = mn_lo == -INFINITY ? 1.f : exp2f(m_lo - mn_lo);      // m = -inf gives 0
+    const float al_hi = mn_hi == -INFINITY ? 1.f : exp2f(m_hi - mn_hi);
+    float ps_lo = 0.f, ps_hi = 0.f;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const float p0v = mn_lo == -INFINITY ? 0.f : exp2f(s[n][0] - mn_lo), p1v = mn_lo == -INFINITY ? 0.f : exp2f(s[n][1] - mn_lo);
+      const float p2v = mn_hi == -INFINITY ? 0.f : exp2f(s[n][2] - mn_hi), p3v = mn_hi == -INFINITY ? 0.f : exp2f(s[n][3] - mn_hi);
+      const uint32_t w_lo = pack_bf16(p0v, p1v), w_hi = pack_bf16(p2v, p3v);
+      // the sums count the weights as the second product will read them: rounded to bf16
+      const float2 f_lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w_lo));
+      const float2 f_hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w_hi));
+      ps_lo += f_lo.x + f_lo.y;
+      ps_hi += f_hi.x + f_hi.y;
+      const int col = warp * 16 + n * 8 + 2 * t4;
+      *reinterpret_cast<uint32_t*>(Ps + r_lo * (CHUNK + PAD) + col) = w_lo;
+      *reinterpret_cast<uint32_t*>(Ps + r_hi * (CHUNK + PAD) + col) = w_hi;
+    }
+    ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 1);
+    ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 2);
+    ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 1);
+    ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 2);
+    if (t4 == 0) {
+      wsum[warp * ROWS + r_lo] = ps_lo;
+      wsum[warp * ROWS + r_hi] = ps_hi;
+    }
+    __syncthreads();
+    l_lo = l_lo * al_lo + ((wsum[r_lo] + wsum[ROWS + r_lo]) + (wsum[2 * ROWS + r_lo] + wsum[3 * ROWS + r_lo]));
+    l_hi = l_hi * al_hi + ((wsum[r_hi] + wsum[ROWS + r_hi]) + (wsum[2 * ROWS + r_hi] + wsum[3 * ROWS + r_hi]));
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+
+    // ---- O = alpha O + P V for this warp's value columns
+#pragma unroll
+    for (int n = 0; n < DVW / 8; ++n) {
+      acc[n][0] *= al_lo; acc[n][1] *= al_lo;
+      acc[n][2] *= al_hi; acc[n][3] *= al_hi;
+    }
+    const bf16* pa = Ps + r_lo * (CHUNK + PAD) + 2 * t4;
+#pragma unroll
+    for (int k0 = 0; k0 < CHUNK; k0 += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(pa + k0);
+      a[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * (CHUNK + PAD) + k0);
+      a[2] = *reinterpret_cast<const uint32_t*>(pa + k0 + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(pa + 8 * (CHUNK + PAD) + k0 + 8);
+      const bf16* vrow = Vrows + (k0 + (lane & 15)) * vpitch + col0;      // lanes 0..15: the 16 keys of this step
+#pragma unroll
+      for (int n = 0; n < DVW / 8; ++n) {
+        if (n < ntiles_v) {
+          uint32_t b0, b1;
+          ldmatrix_x2_trans(b0, b1, vrow + n * 8);
+          mma_bf16(acc[n], a, b0, b1);
+        }
+      }
+    }
+  }
+
+  // ---- the sink joins the denominator once; then the rows are written
+  if (sinks) {
+    const float sk_lo = sinks[row_head(ok_lo ? r_lo : 0)] * LOG2E, sk_hi = sinks[row_head(ok_hi ? r_hi : 0)] * LOG2E;
+    const float mf_lo = fmaxf(m_lo, sk_lo), mf_hi = fmaxf(m_hi, sk_hi);
+    const float keep_lo = m_lo == -INFINITY ? 0.f : exp2f(m_lo - mf_lo), keep_hi = m_hi == -INFINITY ? 0.f : exp2f(m_hi - mf_hi);
+    l_lo = l_lo * keep_lo + exp2f(sk_lo - mf_lo);
+    l_hi = l_hi * keep_hi + exp2f(sk_hi - mf_hi);
+#pragma unroll
+    for (int n = 0; n < DVW / 8; ++n) {
+      acc[n][0] *= keep_lo; acc[n][1] *= keep_lo;
+      acc[n][2] *= keep_hi; acc[n][3] *= keep_hi;
+    }
+  }
+  const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+#pragma unroll
+  for (int n = 0; n < DVW / 8; ++n) {
+    if (n < ntiles_v) {
+      const int col = col0 + n * 8 + 2 * t4;
+      if (ok_lo)
+        *reinterpret_cast<uint32_t*>(out + (size_t)(qs + tok0 + row_token(r_lo)) * out_stride + row_head(r_lo) * dv + col) =
+            pack_bf16(acc[n][0] * inv_lo, acc[n][1] * inv_lo);
+      if (ok_hi)
+        *reinterpret_cast<uint32_t*>(out + (size_t)(qs + tok0 + row_token(r_hi)) * out_stride + row_head(r_hi) * dv + col) =
+            pack_bf16(acc[n][2] * inv_hi, acc[n][3] * inv_hi);
+    }
+  }
+}
+
+// Tokens per tile for a group of G query heads per key/value head, or 0 when the kernel does not
+// take the group size.
+extern "C" int mi_attention_rows_tile_tokens(int G) {
+  if (G <= 0) return 0;
+  if (G >= ROWS) return G % ROWS == 0 ? 1 : 0;
+  return ROWS % G == 0 ? ROWS / G : 0;
+}
+
+extern "C" int mi_attention_rows_supported(int nq, int nkv, int d, int dv, int v_prefix) {
+  if (nq <= 0 || nkv <= 0 || nq % nkv) return 0;
+  if (!mi_attention_rows_tile_tokens(nq / nkv)) return 0;
+  if (d < 16 || d % 16 || d > 1024 || dv < 32 || dv % 32 || dv > 512) return 0;
+  if (v_prefix && dv > d) return 0;
+  return 1;
+}
+
+extern "C" int mi_attention_rows(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
+                                 const void* vcache, const int* block_table, int bt_stride, const int* table_rows,
+                                 int page_size, const int* q_start, const int* q_len, const int* kv_len,
+                                 const int* tile_req, const int* tile_tok0, int n_tiles, int tile_tokens, int nq,
+                                 int nkv, int d, int dv, float scale, const float* sinks, const float* slopes,
+                                 int v_prefix, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (!mi_attention_rows_supported(nq, nkv, d, dv, v_prefix))
+    MI_REFUSE("attention_rows: sizes not taken (heads %d over %d, keys %d, values %d)", nq, nkv, d, dv);
+  const int G = nq / nkv;
+  if (tile_tokens != mi_attention_rows_tile_tokens(G))
+    MI_REFUSE("attention_rows: tiles of %d tokens, this group size wants %d", tile_tokens, mi_attention_rows_tile_tokens(G));
+  if (page_size <= 0) MI_REFUSE("attention_rows: bad page size %d", page_size);
+  if (!v_prefix && !vcache) MI_REFUSE("attention_rows: no value cache");
+  if (!mi_aligned(q, 16) || !mi_aligned(kcache, 16) || !mi_aligned(vcache, 16) || !mi_aligned(out, 4) ||
+      q_stride % 8 || out_stride % 2)
+    MI_REFUSE("attention_rows: q and the caches must be 16-byte aligned with rows of whole 16-byte pieces");
+  const long long blocks = (long long)n_tiles * nkv * (G >= ROWS ? G / ROWS : 1);
+  if (blocks > 0x7fffffffLL) MI_REFUSE("attention_rows: too many blocks for one launch");
+  const size_t smem = ((size_t)(ROWS + CHUNK) * (d + PAD) + (v_prefix ? 0 : (size_t)CHUNK * (dv + PAD)) +
+                       (size_t)ROWS * (CHUNK + PAD)) * sizeof(bf16) +
+                      2 * NWARPS * ROWS * sizeof(float) + 2 * CHUNK * sizeof(int);
+  if (smem > 227 * 1024) MI_REFUSE("attention_rows: keys of %d and values of %d do not fit in shared memory", d, dv);
+#define MI_GO(DVW)                                                                                              \
+  do {                                                                                                          \
+    auto kern = attention_rows_kernel<DVW>;                                                                     \
+    if (smem > 48 * 1024) {                                                                                     \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+      if (e != cudaSuccess) return (int)e;                                                                      \
+    }                                                                                                           \
+    MI_LAUNCH(kern, (unsigned)blocks, NWARPS * 32, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, \
+              (const bf16*)kcache, (const bf16*)vcache, block_table, bt_stride, table_rows, page_size, q_start,  \
+              q_len, kv_len, tile_req, tile_tok0, tile_tokens, nq, nkv, d, dv, scale, sinks, slopes, v_prefix); \
+  } while (0)
+  if (dv <= 128) MI_GO(32);
+  else if (dv <= 256) MI_GO(64);
+  else MI_GO(128);
+#undef MI_GO
+  MI_RETURN_LAUNCH_STATUS();
+}

@@ -44,6 +44,7 @@ LIBRARIES: dict[str, tuple[list[str], list[str], list[str]]] = {
     "moe": (["moe.cu"], ["common.cuh"], []),
     "stream": (["stream.cu"], ["common.cuh"], []),
     "qk_prepare": (["qk_prepare.cu"], ["common.cuh"], []),
+    "attention_rows": (["attention_rows.cu"], ["common.cuh"], []),
 }
 
 

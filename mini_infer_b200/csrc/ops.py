@@ -279,7 +279,17 @@ def _sig_qk_prepare(lib: ctypes.CDLL) -> None:
                                       c_void_p, c_int, c_int, c_int, c_void_p]
 
 
+def _sig_attention_rows(lib: ctypes.CDLL) -> None:
+    lib.mi_attention_rows.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+        c_float, c_void_p, c_void_p, c_int, c_void_p]
+    lib.mi_attention_rows_tile_tokens.argtypes = [c_int]
+    lib.mi_attention_rows_supported.argtypes = [c_int, c_int, c_int, c_int, c_int]
+
+
 _SIGNATURES = {
+    "attention_rows": _sig_attention_rows,
     "stream": _sig_stream,
     "qk_prepare": _sig_qk_prepare,
     "layernorm": _sig_layernorm,
@@ -1696,6 +1706,35 @@ def latent_prepare(packed: torch.Tensor, q_off: int, nq: int, q_head: int, q_rot
     _finish(lib, rc, "latent_prepare")
 
 
+USE_ROWS_ATTENTION = os.environ.get("MINI_INFER_ROWS_ATTENTION", "1") != "0"
+ROWS_ATTENTION_ROWS = 16      # query rows per block of attention_rows.cu (ROWS there)
+
+
+def rows_attention_tile_tokens(group: int) -> int:
+    """Tokens per tile of the tensor-core kernel of ``attention_ext`` for ``group`` query heads per
+    key/value head (16 rows of (token, head in group) per block), or 0 where it does not take the
+    group size.  The same rule as the library's ``mi_attention_rows_tile_tokens``."""
+    if group <= 0:
+        return 0
+    if group >= ROWS_ATTENTION_ROWS:
+        return 1 if group % ROWS_ATTENTION_ROWS == 0 else 0
+    return ROWS_ATTENTION_ROWS // group if ROWS_ATTENTION_ROWS % group == 0 else 0
+
+
+def rows_attention_supported(nq: int, nkv: int, d: int, dv: int, values_in_keys: bool) -> bool:
+    """Whether attention_rows.cu takes these sizes (the library's ``mi_attention_rows_supported``, made
+    here so that a model it does not take never compiles it): keys a multiple of 16 up to 1024,
+    values a multiple of 32 up to 512, a group size that divides 16 or is a multiple of it."""
+    if not USE_ROWS_ATTENTION or nq <= 0 or nkv <= 0 or nq % nkv or not rows_attention_tile_tokens(nq // nkv):
+        return False
+    if d < 16 or d % 16 or d > 1024 or dv < 32 or dv % 32 or dv > 512:
+        return False
+    if values_in_keys and dv > d:
+        return False
+    smem = ((16 + 64) * (d + 8) + (0 if values_in_keys else 64 * (dv + 8)) + 16 * 72) * 2 + 1024
+    return smem <= 227 * 1024
+
+
 def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: int, d: int, dv: int, scale: float, *,
                   window: int = 0, sinks: torch.Tensor | None = None, slopes: torch.Tensor | None = None,
                   values_in_keys: bool = False) -> None:
@@ -1703,7 +1742,9 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
     head that joins the softmax's denominator without a key or a value), ``slopes`` (fp32 ``[nq]``:
     the scaled score of a key ``dist`` positions back is lowered by ``slope * dist``) and
     ``values_in_keys`` (the cache layer has keys only; a key's value is the first ``dv`` numbers of its
-    own row).  fp32 scores, weights and sums for float32 and bfloat16 alike."""
+    own row).  fp32 scores, weights and sums for float32 and bfloat16 alike.  bfloat16 with sizes that
+    attention_rows.cu takes (``rows_attention_supported``) and tiles planned for it runs on tensor
+    cores (weights rounded to bfloat16 for the second product); everything else on CUDA cores."""
     group = ctx.groups[cache.group]
     _cuda(q, out, cache.k, None if values_in_keys else cache.v, sinks, slopes)
     _cols(q, "attention")
@@ -1718,11 +1759,24 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
     if vc is not None and (vc.dtype != q.dtype or vc.dim() != 4 or vc.shape[1:] != (nkv, group.page_size, dv)
                            or not vc.is_contiguous()):
         raise KernelError("attention: the value cache must be contiguous [pages, nkv, page_size, dv] in q's dtype")
+    bt = group.block_table
+    if (q.dtype == torch.bfloat16 and not window and rows_attention_supported(nq, nkv, d, dv, values_in_keys)
+            and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
+            and rows_attention_tile_tokens(nq // nkv) in ctx.tiles):
+        tt = rows_attention_tile_tokens(nq // nkv)
+        tile_req, tile_tok0, n_tiles = ctx.q_tiles(tt)
+        lib = _lib("attention_rows")
+        rc = lib.mi_attention_rows(
+            _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kc), _ptr(vc), _ptr(bt), bt.stride(0),
+            _ptr(group.table_rows), int(group.page_size), _ptr(ctx.q_start), _ptr(ctx.q_len), _ptr(ctx.kv_len),
+            _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), tt, nq, nkv, d, dv, float(scale), _ptr(sinks), _ptr(slopes),
+            1 if values_in_keys else 0, _stream())
+        _finish(lib, rc, "attention")
+        return
     tile_req, tile_tok0, n_tiles = ctx.q_tiles(ATTENTION_TILE_TOKENS)
     lib = _lib("attention_generic")
     if lib.mi_attention_generic_tile_tokens() != ATTENTION_TILE_TOKENS:
         raise KernelError("attention: the kernel's tile size differs from ATTENTION_TILE_TOKENS")
-    bt = group.block_table
     rc = lib.mi_attention_generic_ext(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kc), _ptr(vc), _ptr(bt), bt.stride(0),
         _ptr(group.table_rows), int(group.page_size), _ptr(ctx.q_start), _ptr(ctx.q_len), _ptr(ctx.kv_len),

@@ -92,7 +92,10 @@ class LatentAttention(ProjectedMixer):
         return KVNeed(1, self.rank + self.rd, None, 0)     # keys only: the latent is key and value
 
     def plan_needs(self):
-        return PlanNeeds(frozenset({ops.ATTENTION_TILE_TOKENS}))
+        tiles = {ops.ATTENTION_TILE_TOKENS}
+        if ops.rows_attention_supported(self.heads, 1, self.rank + self.rd, self.rank, True):
+            tiles.add(ops.rows_attention_tile_tokens(self.heads))
+        return PlanNeeds(frozenset(tiles))
 
     def bind(self, tensors, dtype, device):
         names = ["q", "dkv"] + (["g"] if self.gate else [])
@@ -200,7 +203,10 @@ class DistanceBiasAttention(ProjectedMixer):
         return KVNeed(self.nkv, self.d, None, None if self.dv == self.d else self.dv)
 
     def plan_needs(self):
-        return PlanNeeds(frozenset({ops.ATTENTION_TILE_TOKENS}))
+        tiles = {ops.ATTENTION_TILE_TOKENS}
+        if ops.rows_attention_supported(self.nq, self.nkv, self.d, self.dv, False):
+            tiles.add(ops.rows_attention_tile_tokens(self.nq // self.nkv))
+        return PlanNeeds(frozenset(tiles))
 
     def bind(self, tensors, dtype, device):
         names = ["q", "k"] + ([] if self.values_are_keys else ["v"])

@@ -3,7 +3,8 @@
 The configurations differ from one another in every size: one head and several, grouped and
 ungrouped key/value heads, value sizes below and above the key size, sizes that are no multiple of
 4, a rotated part that turns whole or in part, a loop at the start, in the middle and up to the last
-layer, one pass and several, layers with and without a feed-forward, and no loop at all.
+layer, one pass and several, layers with and without a feed-forward, and no loop at all; some take
+the tensor-core attention kernel in bfloat16 (D, E), the others the CUDA-core one.
 """
 
 from __future__ import annotations
@@ -49,12 +50,18 @@ CONFIGS = {
                 vocab=47, width=36, eps=1e-5, buckets=5, mul_prev=2, mul_cur=9, loop=None),
     # a loop of one pass in the middle
     "D": config([biased(heads=2, kv_heads=2, dim=32, scale=0.18, ff=24),
-                 latent(heads=4, dim=16, rot_dim=16, vdim=8, kv_rank=48, base=10000.0, dims=16, scale=0.17, ff=48),
+                 latent(heads=4, dim=16, rot_dim=16, vdim=8, kv_rank=64, base=10000.0, dims=16, scale=0.17, ff=48),
                  biased(heads=8, kv_heads=2, dim=12, scale=0.28, ff=24)],
                 vocab=80, width=48, eps=1e-6, buckets=64, mul_prev=13, mul_cur=1, loop=(1, 2, 1)),
+    # many heads over one key/value head (several blocks of heads per token in the tensor-core kernel),
+    # sizes that kernel takes, a loop over everything
+    "E": config([latent(heads=16, dim=8, rot_dim=16, vdim=12, kv_rank=32, base=500.0, dims=16, scale=0.2, ff=32),
+                 biased(heads=32, kv_heads=1, dim=32, scale=0.15, ff=None),
+                 biased(heads=8, kv_heads=4, dim=64, scale=0.12, ff=32)],
+                vocab=70, width=64, eps=1e-5, buckets=11, mul_prev=5, mul_cur=6, loop=(0, 3, 2)),
 }
 
-PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 32}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 32, "E": 16}
 
 
 def random_state(cfg: dict, seed: int) -> dict[str, torch.Tensor]:

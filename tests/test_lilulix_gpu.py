@@ -18,7 +18,7 @@ from lilulix_configs import CONFIGS, PAGE_SIZE, prompt, random_state
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
-LENGTHS = {"A": [1, 2, 37, 70], "B": [3, 19, 64, 90, 41], "C": [50, 5, 33, 81], "D": [66, 1, 45]}
+LENGTHS = {"A": [1, 2, 37, 70], "B": [3, 19, 64, 90, 41], "C": [50, 5, 33, 81], "D": [66, 1, 45], "E": [130, 7, 65, 64]}
 
 
 def ops():
@@ -430,3 +430,88 @@ def test_values_read_from_the_keys_rows(portions, page):
     got = torch.cat(got).reshape(n, nq, dv)
     assert (got - want).abs().max() <= 2e-5 * max(1.0, want.abs().max())
     assert torch.allclose(got[200:, 1], torch.arange(dv, dtype=torch.float64).expand(100, dv), atol=1e-3)
+
+
+def test_configurations_take_both_attention_kernels():
+    """The tensor-core kernel takes D's and E's sizes, the CUDA-core kernel the others'."""
+    o = ops()
+    taken = {}
+    for which, cfg in CONFIGS.items():
+        flags = []
+        for layer in cfg["layers"]:
+            m = layer["mixer"]
+            if layer["type"] == "latent_attention":
+                flags.append(o.rows_attention_supported(m["heads"], 1, m["kv_rank"] + m["rot_dim"], m["kv_rank"], True))
+            else:
+                flags.append(o.rows_attention_supported(m["heads"], m["kv_heads"], m["dim"], m["dim"], False))
+        taken[which] = flags
+    assert taken["D"] == [True, True, False] and taken["E"] == [True, True, True]
+    assert not any(taken["A"] + taken["B"] + taken["C"])
+
+
+@pytest.mark.parametrize("nq,nkv,d,dv,prefix", [(4, 2, 32, 32, False), (16, 1, 48, 32, True), (32, 2, 64, 64, False),
+                                                (8, 1, 576, 512, True), (1, 1, 16, 32, False), (2, 1, 144, 96, True),
+                                                (8, 8, 128, 256, False)])
+@pytest.mark.parametrize("portions,page", [((333,), 16), ((3, 2, 120, 1, 1, 2, 70, 1), 8), ((64, 64, 1), 64)])
+def test_tensor_core_attention_against_the_plain_softmax(nq, nkv, d, dv, prefix, portions, page):
+    """bfloat16 on the tensor-core kernel: random rows through prompts and single tokens, sinks and
+    slopes per head, values of their own size or read from the keys' rows, against the plain softmax
+    computed from the same bfloat16 rows; one key stands out far back, at a page's border."""
+    o = ops()
+    assert o.rows_attention_supported(nq, nkv, d, dv, prefix)
+    n = sum(portions)
+    q = rnd(n, nq, d, seed=1, scale=d ** -0.25).bfloat16()
+    k = rnd(n, nkv, d, seed=2, scale=d ** -0.25).bfloat16()
+    v = k[:, :, :dv] if prefix else rnd(n, nkv, dv, seed=3).bfloat16()
+    if prefix:
+        k = k.clone()
+    marked = page - 1                               # the last slot of the request's first page
+    k[marked] = 0.0
+    k[marked, :, d - 1] = 6.0
+    if not prefix:
+        v = v.clone()
+        v[marked] = 3.0
+    q[n - 20:, 0] = 0.0
+    q[n - 20:, 0, d - 1] = 5.0                      # head 0's late queries point at the marked key
+    slopes = torch.linspace(0.0, 0.2, nq, dtype=torch.float64)
+    slopes[0] = 0.0
+    sinks = torch.linspace(-3.0, 3.0, nq, dtype=torch.float64)
+    vals = k.double()[:, :, :dv] if prefix else v.double()
+    want = plain_scores_attention(q.double(), k.double(), vals, 0.9, slopes, sinks)
+    G = nq // nkv
+    tt = o.rows_attention_tile_tokens(G)
+    kc = torch.full((-(-n // page) + 1, nkv, page, d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vc = None if prefix else torch.full((kc.shape[0], nkv, page, dv), float("nan"), dtype=torch.bfloat16, device=DEV)
+    pages = list(range(kc.shape[0] - 1, 0, -1))                   # pages handed out from the far end
+    table = torch.full((3, len(pages)), -1, dtype=torch.int32, device=DEV)
+    table[2, :len(pages)] = i32(pages)
+    got, t0 = [], 0
+    for cnt in portions:
+        slots = [pages[p // page] * page + p % page for p in range(t0, t0 + cnt)]
+        by_slot = o.unpack_cache_pages(kc)
+        by_slot[slots] = k[t0:t0 + cnt].to(DEV)
+        kc.copy_(o.pack_cache_pages(by_slot, page))
+        if vc is not None:
+            by_slot = o.unpack_cache_pages(vc)
+            by_slot[slots] = v[t0:t0 + cnt].to(DEV)
+            vc.copy_(o.pack_cache_pages(by_slot, page))
+        tiles = [(0, a) for a in range(0, cnt, tt)]
+        ctx = SimpleNamespace(
+            groups=[SimpleNamespace(block_table=table, page_size=page, table_rows=i32([2]))],
+            q_start=i32([0]), q_len=i32([cnt]), kv_len=i32([t0 + cnt]),
+            tiles={tt: (i32([a for a, _ in tiles]), i32([b for _, b in tiles]), len(tiles))})
+        ctx.q_tiles = lambda size, _c=ctx: _c.tiles[size]
+        cache = SimpleNamespace(group=0, k=kc, v=vc)
+        out = torch.full((cnt, nq * dv), float("nan"), dtype=torch.bfloat16, device=DEV)
+        before = o.launch_count
+        o.attention_ext(q[t0:t0 + cnt].reshape(cnt, -1).to(DEV), out, cache, ctx, nq, nkv, d, dv, 0.9,
+                        sinks=sinks.float().to(DEV), slopes=slopes.float().to(DEV), values_in_keys=prefix)
+        assert o.launch_count == before + 1 and "attention_rows" in o._configured
+        got.append(out.cpu().double())
+        t0 += cnt
+    got = torch.cat(got).reshape(n, nq, dv)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() <= 2e-2 * max(1.0, want.abs().max())
+    late = got[n - 20:, 0]
+    target = k.double()[marked, 0, :dv] if prefix else torch.full((dv,), 3.0, dtype=torch.float64)
+    assert (late - target).abs().max() <= 2e-2 * max(1.0, target.abs().max())
