@@ -4,14 +4,20 @@
 // own rows, a sink score per head in the softmax's denominator, and a distance bias with a slope per
 // head.  Prompt portions and single decoded tokens alike.
 //
-// A block of four warps takes 16 query rows that share one key/value head: with G = nq / nkv query
-// heads per key/value head, the rows are (token, head in group) pairs, 16 / G tokens by G heads when
-// G divides 16, or 16 of the G heads of one token when 16 divides G.  It walks the request's keys in
-// chunks of 64 (cut at absolute multiples of 64): the chunk's rows are gathered from their pages into
-// shared memory (un-permuted), warp w computes the scores of keys 16 w .. 16 w + 15 for all 16 rows
-// (S = Q K^T), the warps exchange row maxima and sums and the bf16 weights through shared memory,
-// and each warp then adds P V for its quarter of the value columns to accumulators in registers.
-// Scores, the softmax and all sums are fp32; the weights are rounded to bf16 for the second product.
+// A block takes R = 16 MT query rows that share one key/value head (MT = 1: four warps, for steps of
+// single tokens; MT = 4: sixteen warps, for prompt portions): with G = nq / nkv query heads per
+// key/value head, the rows are (token, head in group) pairs, R / G tokens by G heads when G divides
+// R, or R of the G heads of one token when R divides G.  It walks the request's keys in chunks of 64
+// (cut at absolute multiples of 64): the chunk's rows are gathered from their pages into shared
+// memory (un-permuted); each group of four warps owns 16 of the rows, and in it warp w computes the
+// scores of keys 16 w .. 16 w + 15 (S = Q K^T), the four exchange row maxima and sums and the bf16
+// weights through shared memory, and each then adds P V for its quarter of the value columns to
+// accumulators in registers.  Scores, the softmax and all sums are fp32; the weights are rounded to
+// bf16 for the second product.
+//
+// With n_splits > 1 the keys of every tile are cut into that many runs of whole chunks, one block
+// each; the blocks leave unnormalised sums with their maxima and denominators in `part_o` / `part_ml`
+// and attention_rows_merge_kernel adds them up (and the sink) in a fixed order.
 //
 // Layouts as in attention_generic.cu: q [tokens, q_stride], out [tokens, out_stride], kcache
 // [pages, nkv, page_size, d], vcache [pages, nkv, page_size, dv] (null with v_prefix), block tables
@@ -20,9 +26,9 @@
 
 MI_DEFINE_ERROR_API()
 
-#define ROWS 16
+#define ROWS 16      // rows of one group of four warps
 #define CHUNK 64
-#define NWARPS 4
+#define QUARTERS 4   // warps of a group: each takes a quarter of a chunk's keys and of the value columns
 #define PAD 8   // bf16 elements behind every shared-memory row: rows stay 16-byte aligned, banks spread
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -41,33 +47,45 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Which token (within the tile) and which head a row of a tile of R rows stands for.
+struct RowMap {
+  int G, R, kvh, hs;
+  __device__ __forceinline__ int token(int r) const { return G >= R ? 0 : r / G; }
+  __device__ __forceinline__ int head(int r) const { return G >= R ? kvh * G + hs * R + r : kvh * G + r % G; }
+};
+
 // DVW: value columns per warp that the accumulators have room for (dv <= 4 * DVW).
-template <int DVW>
-__global__ void __launch_bounds__(NWARPS * 32)
+template <int DVW, int MT>
+__global__ void __launch_bounds__(QUARTERS * MT * 32)
 attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                       const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                       const int* __restrict__ block_table, int bt_stride, const int* __restrict__ table_rows,
                       int page_size, const int* __restrict__ q_start, const int* __restrict__ q_len,
                       const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                       const int* __restrict__ tile_tok0, int tile_tokens, int nq, int nkv, int d, int dv, float scale,
-                      const float* __restrict__ sinks, const float* __restrict__ slopes, int v_prefix) {
+                      const float* __restrict__ sinks, const float* __restrict__ slopes, int v_prefix,
+                      int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
   mi_pdl_enter();
+  constexpr int R = ROWS * MT, NW = QUARTERS * MT, NT = NW * 32;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int dp = d + PAD, dvp = dv + PAD;
-  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [ROWS][dp]
-  bf16* Ks = Qs + ROWS * dp;                                    // [CHUNK][dp]
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [R][dp]
+  bf16* Ks = Qs + R * dp;                                       // [CHUNK][dp]
   bf16* Vs = Ks + CHUNK * dp;                                   // [CHUNK][dvp] (nothing with v_prefix)
-  bf16* Ps = v_prefix ? Vs : Vs + CHUNK * dvp;                  // [ROWS][CHUNK + PAD]
-  float* wmax = reinterpret_cast<float*>(Ps + ROWS * (CHUNK + PAD));   // [NWARPS][ROWS]
-  float* wsum = wmax + NWARPS * ROWS;                           // [NWARPS][ROWS]
-  int* rowbase = reinterpret_cast<int*>(wsum + NWARPS * ROWS);  // [CHUNK] cache row of each key, -1: none
+  bf16* Ps = v_prefix ? Vs : Vs + CHUNK * dvp;                  // [R][CHUNK + PAD]
+  float* wmax = reinterpret_cast<float*>(Ps + R * (CHUNK + PAD));      // [QUARTERS][R]
+  float* wsum = wmax + QUARTERS * R;                            // [QUARTERS][R]
+  int* rowbase = reinterpret_cast<int*>(wsum + QUARTERS * R);   // [CHUNK] cache row of each key, -1: none
   int* rowoff = rowbase + CHUNK;                                // [CHUNK] in-page offset of each key
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = (tid >> 5) % QUARTERS, mt = (tid >> 5) / QUARTERS;   // the quarter, and which 16 rows
   const int g = lane >> 2, t4 = lane & 3;                      // the fragment's row (and row + 8) and column pair
   const int G = nq / nkv;
-  const int head_tiles = G >= ROWS ? G / ROWS : 1;
+  const int head_tiles = G >= R ? G / R : 1;
   int bid = blockIdx.x;
+  const int split = bid % n_splits;
+  bid /= n_splits;
   const int hs = bid % head_tiles;
   bid /= head_tiles;
   const int kvh = bid % nkv;
@@ -79,13 +97,16 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
   const int p0 = kl - ql + tok0;                                // position of the tile's first token
   const int j_end = p0 + nt;                                    // one past the last key any row sees
 
-  // a row's token (within the tile) and head
-  auto row_token = [&](int r) { return G >= ROWS ? 0 : r / G; };
-  auto row_head = [&](int r) { return G >= ROWS ? kvh * G + hs * ROWS + r : kvh * G + r % G; };
+  const RowMap rows{G, R, kvh, hs};
+  auto row_token = [&](int r) { return rows.token(r); };
+  auto row_head = [&](int r) { return rows.head(r); };
+  // this block's run of keys: whole chunks, the same cut for every row of the tile
+  const int chunks_all = (j_end + CHUNK - 1) / CHUNK, chunks_mine = (chunks_all + n_splits - 1) / n_splits;
+  const int j_begin = split * chunks_mine * CHUNK, j_stop = min(j_end, (split + 1) * chunks_mine * CHUNK);
 
   // ---- the queries: 16-byte pieces, zero for rows without a token
   const int pieces = d >> 3;
-  for (int idx = tid; idx < ROWS * pieces; idx += NWARPS * 32) {
+  for (int idx = tid; idx < R * pieces; idx += NT) {
     const int r = idx / pieces, c = idx - r * pieces;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (row_token(r) < nt)
@@ -94,7 +115,7 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
   }
 
   // per thread: the two rows of its fragments
-  const int r_lo = g, r_hi = g + 8;
+  const int r_lo = mt * ROWS + g, r_hi = r_lo + 8;
   const bool ok_lo = row_token(r_lo) < nt, ok_hi = row_token(r_hi) < nt;
   const int pos_lo = p0 + row_token(r_lo), pos_hi = p0 + row_token(r_hi);
   const float slope_lo = slopes ? slopes[row_head(r_lo)] : 0.f, slope_hi = slopes ? slopes[row_head(r_hi)] : 0.f;
@@ -103,13 +124,13 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
   float acc[DVW / 8][4];
 #pragma unroll
   for (int n = 0; n < DVW / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
-  const int col0 = warp * (dv / NWARPS);                        // this warp's value columns
-  const int ntiles_v = (dv / NWARPS) >> 3;
+  const int col0 = warp * (dv / QUARTERS);                      // this warp's value columns
+  const int ntiles_v = (dv / QUARTERS) >> 3;
   const int mk = mi_swizzle_mask_rows(d, 2), mv = mi_swizzle_mask_rows(dv, 2);
   const bf16* Vrows = v_prefix ? Ks : Vs;
   const int vpitch = v_prefix ? dp : dvp;
 
-  for (int j0 = 0; j0 < j_end; j0 += CHUNK) {
+  for (int j0 = j_begin; j0 < j_stop; j0 += CHUNK) {
     __syncthreads();                                            // the chunk before is consumed (first time: Qs written)
     if (tid < CHUNK) {
       const int j = j0 + tid;
@@ -122,7 +143,7 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
       rowoff[tid] = j % page_size;
     }
     __syncthreads();
-    for (int idx = tid; idx < CHUNK * pieces; idx += NWARPS * 32) {
+    for (int idx = tid; idx < CHUNK * pieces; idx += NT) {
       const int jj = idx / pieces, c = idx - jj * pieces;
       const int base = rowbase[jj];
       uint4 v = make_uint4(0, 0, 0, 0);
@@ -131,7 +152,7 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
     }
     if (!v_prefix) {
       const int vpieces = dv >> 3;
-      for (int idx = tid; idx < CHUNK * vpieces; idx += NWARPS * 32) {
+      for (int idx = tid; idx < CHUNK * vpieces; idx += NT) {
         const int jj = idx / vpieces, c = idx - jj * vpieces;
         const int base = rowbase[jj];
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -175,15 +196,15 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
     if (t4 == 0) {
-      wmax[warp * ROWS + r_lo] = mx_lo;
-      wmax[warp * ROWS + r_hi] = mx_hi;
+      wmax[warp * R + r_lo] = mx_lo;
+      wmax[warp * R + r_hi] = mx_hi;
     }
     __syncthreads();
     float cm_lo = wmax[r_lo], cm_hi = wmax[r_hi];
 #pragma unroll
-    for (int w = 1; w < NWARPS; ++w) {
-      cm_lo = fmaxf(cm_lo, wmax[w * ROWS + r_lo]);
-      cm_hi = fmaxf(cm_hi, wmax[w * ROWS + r_hi]);
+    for (int w = 1; w < QUARTERS; ++w) {
+      cm_lo = fmaxf(cm_lo, wmax[w * R + r_lo]);
+      cm_hi = fmaxf(cm_hi, wmax[w * R + r_hi]);
     }
     const float mn_lo = fmaxf(m_lo, cm_lo), mn_hi = fmaxf(m_hi, cm_hi);
     const float al_lo = mn_lo == -INFINITY ? 1.f : exp2f(m_lo - mn_lo);      // m = -inf gives 0
@@ -208,12 +229,12 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
     ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 1);
     ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 2);
     if (t4 == 0) {
-      wsum[warp * ROWS + r_lo] = ps_lo;
-      wsum[warp * ROWS + r_hi] = ps_hi;
+      wsum[warp * R + r_lo] = ps_lo;
+      wsum[warp * R + r_hi] = ps_hi;
     }
     __syncthreads();
-    l_lo = l_lo * al_lo + ((wsum[r_lo] + wsum[ROWS + r_lo]) + (wsum[2 * ROWS + r_lo] + wsum[3 * ROWS + r_lo]));
-    l_hi = l_hi * al_hi + ((wsum[r_hi] + wsum[ROWS + r_hi]) + (wsum[2 * ROWS + r_hi] + wsum[3 * ROWS + r_hi]));
+    l_lo = l_lo * al_lo + ((wsum[r_lo] + wsum[R + r_lo]) + (wsum[2 * R + r_lo] + wsum[3 * R + r_lo]));
+    l_hi = l_hi * al_hi + ((wsum[r_hi] + wsum[R + r_hi]) + (wsum[2 * R + r_hi] + wsum[3 * R + r_hi]));
     m_lo = mn_lo;
     m_hi = mn_hi;
 
@@ -243,6 +264,25 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
     }
   }
 
+  if (n_splits > 1) {
+    // ---- one of several runs of keys: unnormalised sums, maximum and denominator for the merge
+    const size_t unit = (size_t)(blockIdx.x / n_splits) * n_splits + split;
+    float* po = part_o + unit * R * dv;
+    float* pml = part_ml + unit * R * 2;
+#pragma unroll
+    for (int n = 0; n < DVW / 8; ++n) {
+      if (n < ntiles_v) {
+        const int col = col0 + n * 8 + 2 * t4;
+        *reinterpret_cast<float2*>(po + (size_t)r_lo * dv + col) = make_float2(acc[n][0], acc[n][1]);
+        *reinterpret_cast<float2*>(po + (size_t)r_hi * dv + col) = make_float2(acc[n][2], acc[n][3]);
+      }
+    }
+    if (warp == 0 && t4 == 0) {
+      pml[2 * r_lo] = m_lo; pml[2 * r_lo + 1] = l_lo;
+      pml[2 * r_hi] = m_hi; pml[2 * r_hi + 1] = l_hi;
+    }
+    return;
+  }
   // ---- the sink joins the denominator once; then the rows are written
   if (sinks) {
     const float sk_lo = sinks[row_head(ok_lo ? r_lo : 0)] * LOG2E, sk_hi = sinks[row_head(ok_hi ? r_hi : 0)] * LOG2E;
@@ -271,59 +311,133 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
   }
 }
 
-// Tokens per tile for a group of G query heads per key/value head, or 0 when the kernel does not
-// take the group size.
-extern "C" int mi_attention_rows_tile_tokens(int G) {
-  if (G <= 0) return 0;
-  if (G >= ROWS) return G % ROWS == 0 ? 1 : 0;
-  return ROWS % G == 0 ? ROWS / G : 0;
+// Adds up the runs of keys of every row: grid = units x R rows, one block per row.
+__global__ void __launch_bounds__(128)
+attention_rows_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
+                            int out_stride, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                            const int* __restrict__ tile_req, const int* __restrict__ tile_tok0, int tile_tokens,
+                            int nq, int nkv, int dv, const float* __restrict__ sinks, int n_splits, int R) {
+  mi_pdl_enter();
+  constexpr float LOG2E = 1.4426950408889634f;
+  const int r = blockIdx.x % R;
+  int bid = blockIdx.x / R;
+  const int unit = bid;
+  const int G = nq / nkv;
+  const int head_tiles = G >= R ? G / R : 1;
+  const int hs = bid % head_tiles;
+  bid /= head_tiles;
+  const int kvh = bid % nkv;
+  const int tile = bid / nkv;
+  const RowMap rows{G, R, kvh, hs};
+  const int b = tile_req[tile], tok0 = tile_tok0[tile];
+  const int nt = min(tile_tokens, q_len[b] - tok0);
+  if (rows.token(r) >= nt) return;
+  const int head = rows.head(r);
+  const float* pml = part_ml + ((size_t)unit * n_splits * R + r) * 2;
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, pml[(size_t)s * R * 2]);
+  float mf = m;
+  if (sinks) mf = fmaxf(m, sinks[head] * LOG2E);
+  float l = sinks ? exp2f(sinks[head] * LOG2E - mf) : 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = pml[(size_t)s * R * 2];
+    if (ms != -INFINITY) l += pml[(size_t)s * R * 2 + 1] * exp2f(ms - mf);
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  bf16* o = out + (size_t)(q_start[b] + tok0 + rows.token(r)) * out_stride + head * dv;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    float sum = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = pml[(size_t)s * R * 2];
+      if (ms != -INFINITY) sum += part_o[(((size_t)unit * n_splits + s) * R + r) * dv + c] * exp2f(ms - mf);
+    }
+    o[c] = __float2bfloat16_rn(sum * inv);
+  }
+}
+
+// Tokens per tile of `rows` rows for a group of G query heads per key/value head, or 0 when the
+// kernel does not take the group size.
+extern "C" int mi_attention_rows_tile_tokens(int G, int rows) {
+  if (G <= 0 || (rows != ROWS && rows != 4 * ROWS)) return 0;
+  if (G >= rows) return G % rows == 0 ? 1 : 0;
+  return rows % G == 0 ? rows / G : 0;
 }
 
 extern "C" int mi_attention_rows_supported(int nq, int nkv, int d, int dv, int v_prefix) {
   if (nq <= 0 || nkv <= 0 || nq % nkv) return 0;
-  if (!mi_attention_rows_tile_tokens(nq / nkv)) return 0;
+  if (!mi_attention_rows_tile_tokens(nq / nkv, ROWS)) return 0;
   if (d < 16 || d % 16 || d > 1024 || dv < 32 || dv % 32 || dv > 512) return 0;
   if (v_prefix && dv > d) return 0;
   return 1;
 }
 
+// Floats of part_o and of part_ml that a launch with these numbers needs.
+extern "C" int mi_attention_rows_scratch(int n_tiles, int rows, int nq, int nkv, int dv, int n_splits,
+                                         long long* o_floats, long long* ml_floats) {
+  const int G = nq / nkv;
+  const long long units = (long long)n_tiles * nkv * (G >= rows ? G / rows : 1);
+  *o_floats = n_splits > 1 ? units * n_splits * rows * dv : 0;
+  *ml_floats = n_splits > 1 ? units * n_splits * rows * 2 : 0;
+  return 0;
+}
+
 extern "C" int mi_attention_rows(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
                                  const void* vcache, const int* block_table, int bt_stride, const int* table_rows,
                                  int page_size, const int* q_start, const int* q_len, const int* kv_len,
-                                 const int* tile_req, const int* tile_tok0, int n_tiles, int tile_tokens, int nq,
-                                 int nkv, int d, int dv, float scale, const float* sinks, const float* slopes,
-                                 int v_prefix, cudaStream_t stream) {
+                                 const int* tile_req, const int* tile_tok0, int n_tiles, int tile_tokens, int rows,
+                                 int nq, int nkv, int d, int dv, float scale, const float* sinks, const float* slopes,
+                                 int v_prefix, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (!mi_attention_rows_supported(nq, nkv, d, dv, v_prefix))
     MI_REFUSE("attention_rows: sizes not taken (heads %d over %d, keys %d, values %d)", nq, nkv, d, dv);
   const int G = nq / nkv;
-  if (tile_tokens != mi_attention_rows_tile_tokens(G))
-    MI_REFUSE("attention_rows: tiles of %d tokens, this group size wants %d", tile_tokens, mi_attention_rows_tile_tokens(G));
+  if (!mi_attention_rows_tile_tokens(G, rows) || tile_tokens != mi_attention_rows_tile_tokens(G, rows))
+    MI_REFUSE("attention_rows: tiles of %d tokens and %d rows do not fit a group of %d heads", tile_tokens, rows, G);
   if (page_size <= 0) MI_REFUSE("attention_rows: bad page size %d", page_size);
   if (!v_prefix && !vcache) MI_REFUSE("attention_rows: no value cache");
+  if (n_splits < 1 || (n_splits > 1 && (!part_o || !part_ml))) MI_REFUSE("attention_rows: several runs of keys need scratch");
   if (!mi_aligned(q, 16) || !mi_aligned(kcache, 16) || !mi_aligned(vcache, 16) || !mi_aligned(out, 4) ||
-      q_stride % 8 || out_stride % 2)
+      !mi_aligned(part_o, 8) || q_stride % 8 || out_stride % 2)
     MI_REFUSE("attention_rows: q and the caches must be 16-byte aligned with rows of whole 16-byte pieces");
-  const long long blocks = (long long)n_tiles * nkv * (G >= ROWS ? G / ROWS : 1);
-  if (blocks > 0x7fffffffLL) MI_REFUSE("attention_rows: too many blocks for one launch");
-  const size_t smem = ((size_t)(ROWS + CHUNK) * (d + PAD) + (v_prefix ? 0 : (size_t)CHUNK * (dv + PAD)) +
-                       (size_t)ROWS * (CHUNK + PAD)) * sizeof(bf16) +
-                      2 * NWARPS * ROWS * sizeof(float) + 2 * CHUNK * sizeof(int);
+  const long long units = (long long)n_tiles * nkv * (G >= rows ? G / rows : 1);
+  const long long blocks = units * n_splits;
+  if (blocks > 0x7fffffffLL || units * rows > 0x7fffffffLL) MI_REFUSE("attention_rows: too many blocks for one launch");
+  const size_t smem = ((size_t)(rows + CHUNK) * (d + PAD) + (v_prefix ? 0 : (size_t)CHUNK * (dv + PAD)) +
+                       (size_t)rows * (CHUNK + PAD)) * sizeof(bf16) +
+                      2 * QUARTERS * rows * sizeof(float) + 2 * CHUNK * sizeof(int);
   if (smem > 227 * 1024) MI_REFUSE("attention_rows: keys of %d and values of %d do not fit in shared memory", d, dv);
-#define MI_GO(DVW)                                                                                              \
+#define MI_GO(DVW, MT)                                                                                          \
   do {                                                                                                          \
-    auto kern = attention_rows_kernel<DVW>;                                                                     \
+    auto kern = attention_rows_kernel<DVW, MT>;                                                                 \
     if (smem > 48 * 1024) {                                                                                     \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
       if (e != cudaSuccess) return (int)e;                                                                      \
     }                                                                                                           \
-    MI_LAUNCH(kern, (unsigned)blocks, NWARPS * 32, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, \
-              (const bf16*)kcache, (const bf16*)vcache, block_table, bt_stride, table_rows, page_size, q_start,  \
-              q_len, kv_len, tile_req, tile_tok0, tile_tokens, nq, nkv, d, dv, scale, sinks, slopes, v_prefix); \
+    MI_LAUNCH(kern, (unsigned)blocks, QUARTERS * MT * 32, smem, stream, (const bf16*)q, q_stride, (bf16*)out,    \
+              out_stride, (const bf16*)kcache, (const bf16*)vcache, block_table, bt_stride, table_rows, page_size, \
+              q_start, q_len, kv_len, tile_req, tile_tok0, tile_tokens, nq, nkv, d, dv, scale, sinks, slopes,    \
+              v_prefix, n_splits, part_o, part_ml);                                                             \
   } while (0)
-  if (dv <= 128) MI_GO(32);
-  else if (dv <= 256) MI_GO(64);
-  else MI_GO(128);
+  if (rows == ROWS) {
+    if (dv <= 128) MI_GO(32, 1);
+    else if (dv <= 256) MI_GO(64, 1);
+    else MI_GO(128, 1);
+  } else {
+    if (dv <= 128) MI_GO(32, 4);
+    else if (dv <= 256) MI_GO(64, 4);
+    else MI_GO(128, 4);
+  }
 #undef MI_GO
+  {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      snprintf(g_mi_error, sizeof(g_mi_error), "CUDA: %s", cudaGetErrorString(e));
+      return (int)e;
+    }
+  }
+  if (n_splits > 1)
+    MI_LAUNCH(attention_rows_merge_kernel, (unsigned)(units * rows), 128, 0, stream, (const float*)part_o,
+              (const float*)part_ml, (bf16*)out, out_stride, q_start, q_len, tile_req, tile_tok0, tile_tokens, nq, nkv,
+              dv, sinks, n_splits, rows);
   MI_RETURN_LAUNCH_STATUS();
 }

@@ -282,9 +282,9 @@ def _sig_qk_prepare(lib: ctypes.CDLL) -> None:
 def _sig_attention_rows(lib: ctypes.CDLL) -> None:
     lib.mi_attention_rows.argtypes = [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-        c_float, c_void_p, c_void_p, c_int, c_void_p]
-    lib.mi_attention_rows_tile_tokens.argtypes = [c_int]
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+        c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]
+    lib.mi_attention_rows_tile_tokens.argtypes = [c_int, c_int]
     lib.mi_attention_rows_supported.argtypes = [c_int, c_int, c_int, c_int, c_int]
 
 
@@ -1707,32 +1707,60 @@ def latent_prepare(packed: torch.Tensor, q_off: int, nq: int, q_head: int, q_rot
 
 
 USE_ROWS_ATTENTION = os.environ.get("MINI_INFER_ROWS_ATTENTION", "1") != "0"
-ROWS_ATTENTION_ROWS = 16      # query rows per block of attention_rows.cu (ROWS there)
+ROWS_ATTENTION_ROWS = (16, 64)   # query rows per block of attention_rows.cu: steps of single tokens, prompt portions
 
 
-def rows_attention_tile_tokens(group: int) -> int:
+def rows_attention_tile_tokens(group: int, rows: int = 16) -> int:
     """Tokens per tile of the tensor-core kernel of ``attention_ext`` for ``group`` query heads per
-    key/value head (16 rows of (token, head in group) per block), or 0 where it does not take the
-    group size.  The same rule as the library's ``mi_attention_rows_tile_tokens``."""
-    if group <= 0:
+    key/value head and blocks of ``rows`` rows of (token, head in group), or 0 where it does not take
+    the group size.  The same rule as the library's ``mi_attention_rows_tile_tokens``."""
+    if group <= 0 or rows not in ROWS_ATTENTION_ROWS:
         return 0
-    if group >= ROWS_ATTENTION_ROWS:
-        return 1 if group % ROWS_ATTENTION_ROWS == 0 else 0
-    return ROWS_ATTENTION_ROWS // group if ROWS_ATTENTION_ROWS % group == 0 else 0
+    if group >= rows:
+        return 1 if group % rows == 0 else 0
+    return rows // group if rows % group == 0 else 0
+
+
+def rows_attention_tile_sizes(nq: int, nkv: int, d: int, dv: int, values_in_keys: bool) -> frozenset[int]:
+    """The query tile sizes a step must plan for a mixer that wants ``attention_ext`` to use the
+    tensor-core kernel (empty where the kernel does not take the sizes)."""
+    if not rows_attention_supported(nq, nkv, d, dv, values_in_keys):
+        return frozenset()
+    return frozenset(t for t in (rows_attention_tile_tokens(nq // nkv, r) for r in ROWS_ATTENTION_ROWS) if t)
 
 
 def rows_attention_supported(nq: int, nkv: int, d: int, dv: int, values_in_keys: bool) -> bool:
     """Whether attention_rows.cu takes these sizes (the library's ``mi_attention_rows_supported``, made
     here so that a model it does not take never compiles it): keys a multiple of 16 up to 1024,
     values a multiple of 32 up to 512, a group size that divides 16 or is a multiple of it."""
-    if not USE_ROWS_ATTENTION or nq <= 0 or nkv <= 0 or nq % nkv or not rows_attention_tile_tokens(nq // nkv):
+    if not USE_ROWS_ATTENTION or nq <= 0 or nkv <= 0 or nq % nkv or not rows_attention_tile_tokens(nq // nkv, 16):
         return False
     if d < 16 or d % 16 or d > 1024 or dv < 32 or dv % 32 or dv > 512:
         return False
     if values_in_keys and dv > d:
         return False
-    smem = ((16 + 64) * (d + 8) + (0 if values_in_keys else 64 * (dv + 8)) + 16 * 72) * 2 + 1024
-    return smem <= 227 * 1024
+    return _rows_attention_smem(16, d, dv, values_in_keys) <= 227 * 1024
+
+
+def _rows_attention_smem(rows: int, d: int, dv: int, values_in_keys: bool) -> int:
+    return ((rows + 64) * (d + 8) + (0 if values_in_keys else 64 * (dv + 8)) + rows * 72) * 2 + 32 * rows + 512
+
+
+def _rows_attention_plan(ctx, nq: int, nkv: int, d: int, dv: int, values_in_keys: bool, device) -> tuple[int, int, int]:
+    """``(rows per block, tokens per tile, runs of keys per tile)`` for this step: steps of single
+    tokens take 16 rows and cut every request's keys into runs, so that the blocks fill the GPU;
+    prompt portions take 64 rows where the group size and shared memory allow."""
+    group = nq // nkv
+    if not getattr(ctx, "decode_only", False):
+        tt = rows_attention_tile_tokens(group, 64)
+        if tt and tt in ctx.tiles and _rows_attention_smem(64, d, dv, values_in_keys) <= 227 * 1024:
+            return 64, tt, 1
+        return 16, rows_attention_tile_tokens(group, 16), 1
+    tt = rows_attention_tile_tokens(group, 16)
+    units = ctx.tiles[tt][2] * nkv * max(1, group // 16)
+    chunks = max(1, -(-int(getattr(ctx, "max_kv_len", 0) or 64) // 64))
+    splits = max(1, min(-(-2 * _sms(device) // units), chunks, 64))
+    return 16, tt, splits
 
 
 def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: int, d: int, dv: int, scale: float, *,
@@ -1745,6 +1773,7 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
     own row).  fp32 scores, weights and sums for float32 and bfloat16 alike.  bfloat16 with sizes that
     attention_rows.cu takes (``rows_attention_supported``) and tiles planned for it runs on tensor
     cores (weights rounded to bfloat16 for the second product); everything else on CUDA cores."""
+    global launch_count
     group = ctx.groups[cache.group]
     _cuda(q, out, cache.k, None if values_in_keys else cache.v, sinks, slopes)
     _cols(q, "attention")
@@ -1762,16 +1791,23 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
     bt = group.block_table
     if (q.dtype == torch.bfloat16 and not window and rows_attention_supported(nq, nkv, d, dv, values_in_keys)
             and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
-            and rows_attention_tile_tokens(nq // nkv) in ctx.tiles):
-        tt = rows_attention_tile_tokens(nq // nkv)
+            and rows_attention_tile_tokens(nq // nkv, 16) in ctx.tiles):
+        rows, tt, splits = _rows_attention_plan(ctx, nq, nkv, d, dv, values_in_keys, q.device)
         tile_req, tile_tok0, n_tiles = ctx.q_tiles(tt)
+        part_o = part_ml = None
+        if splits > 1:
+            units = n_tiles * nkv * max(1, (nq // nkv) // rows)
+            part_o = torch.empty(units * splits * rows * dv, dtype=torch.float32, device=q.device)
+            part_ml = torch.empty(units * splits * rows * 2, dtype=torch.float32, device=q.device)
         lib = _lib("attention_rows")
         rc = lib.mi_attention_rows(
             _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kc), _ptr(vc), _ptr(bt), bt.stride(0),
             _ptr(group.table_rows), int(group.page_size), _ptr(ctx.q_start), _ptr(ctx.q_len), _ptr(ctx.kv_len),
-            _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), tt, nq, nkv, d, dv, float(scale), _ptr(sinks), _ptr(slopes),
-            1 if values_in_keys else 0, _stream())
+            _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), tt, rows, nq, nkv, d, dv, float(scale), _ptr(sinks),
+            _ptr(slopes), 1 if values_in_keys else 0, splits, _ptr(part_o), _ptr(part_ml), _stream())
         _finish(lib, rc, "attention")
+        if splits > 1:
+            launch_count += 1        # the merge of the runs
         return
     tile_req, tile_tok0, n_tiles = ctx.q_tiles(ATTENTION_TILE_TOKENS)
     lib = _lib("attention_generic")

@@ -92,9 +92,7 @@ class LatentAttention(ProjectedMixer):
         return KVNeed(1, self.rank + self.rd, None, 0)     # keys only: the latent is key and value
 
     def plan_needs(self):
-        tiles = {ops.ATTENTION_TILE_TOKENS}
-        if ops.rows_attention_supported(self.heads, 1, self.rank + self.rd, self.rank, True):
-            tiles.add(ops.rows_attention_tile_tokens(self.heads))
+        tiles = {ops.ATTENTION_TILE_TOKENS} | ops.rows_attention_tile_sizes(self.heads, 1, self.rank + self.rd, self.rank, True)
         return PlanNeeds(frozenset(tiles))
 
     def bind(self, tensors, dtype, device):
@@ -203,9 +201,7 @@ class DistanceBiasAttention(ProjectedMixer):
         return KVNeed(self.nkv, self.d, None, None if self.dv == self.d else self.dv)
 
     def plan_needs(self):
-        tiles = {ops.ATTENTION_TILE_TOKENS}
-        if ops.rows_attention_supported(self.nq, self.nkv, self.d, self.dv, False):
-            tiles.add(ops.rows_attention_tile_tokens(self.nq // self.nkv))
+        tiles = {ops.ATTENTION_TILE_TOKENS} | ops.rows_attention_tile_sizes(self.nq, self.nkv, self.d, self.dv, False)
         return PlanNeeds(frozenset(tiles))
 
     def bind(self, tensors, dtype, device):

@@ -452,8 +452,9 @@ def test_configurations_take_both_attention_kernels():
 @pytest.mark.parametrize("nq,nkv,d,dv,prefix", [(4, 2, 32, 32, False), (16, 1, 48, 32, True), (32, 2, 64, 64, False),
                                                 (8, 1, 576, 512, True), (1, 1, 16, 32, False), (2, 1, 144, 96, True),
                                                 (8, 8, 128, 256, False)])
-@pytest.mark.parametrize("portions,page", [((333,), 16), ((3, 2, 120, 1, 1, 2, 70, 1), 8), ((64, 64, 1), 64)])
-def test_tensor_core_attention_against_the_plain_softmax(nq, nkv, d, dv, prefix, portions, page):
+@pytest.mark.parametrize("portions,page,mode", [((333,), 16, "rows64"), ((3, 2, 120, 1, 1, 2, 70, 1), 8, "rows16"),
+                                                ((64, 64, 1), 64, "rows64"), ((200, 1, 1, 67, 1), 16, "runs")])
+def test_tensor_core_attention_against_the_plain_softmax(nq, nkv, d, dv, prefix, portions, page, mode):
     """bfloat16 on the tensor-core kernel: random rows through prompts and single tokens, sinks and
     slopes per head, values of their own size or read from the keys' rows, against the plain softmax
     computed from the same bfloat16 rows; one key stands out far back, at a page's border."""
@@ -479,7 +480,9 @@ def test_tensor_core_attention_against_the_plain_softmax(nq, nkv, d, dv, prefix,
     vals = k.double()[:, :, :dv] if prefix else v.double()
     want = plain_scores_attention(q.double(), k.double(), vals, 0.9, slopes, sinks)
     G = nq // nkv
-    tt = o.rows_attention_tile_tokens(G)
+    # blocks of 16 rows, blocks of 64 rows, or 16 rows with every tile's keys cut into runs that are merged
+    tt16, tt64 = o.rows_attention_tile_tokens(G, 16), o.rows_attention_tile_tokens(G, 64)
+    tt = tt64 if mode == "rows64" and tt64 else tt16
     kc = torch.full((-(-n // page) + 1, nkv, page, d), float("nan"), dtype=torch.bfloat16, device=DEV)
     vc = None if prefix else torch.full((kc.shape[0], nkv, page, dv), float("nan"), dtype=torch.bfloat16, device=DEV)
     pages = list(range(kc.shape[0] - 1, 0, -1))                   # pages handed out from the far end
@@ -495,18 +498,23 @@ def test_tensor_core_attention_against_the_plain_softmax(nq, nkv, d, dv, prefix,
             by_slot = o.unpack_cache_pages(vc)
             by_slot[slots] = v[t0:t0 + cnt].to(DEV)
             vc.copy_(o.pack_cache_pages(by_slot, page))
-        tiles = [(0, a) for a in range(0, cnt, tt)]
+        tiles = {}
+        for size in {tt, tt16}:
+            firsts = list(range(0, cnt, size))
+            tiles[size] = (i32([0] * len(firsts)), i32(firsts), len(firsts))
         ctx = SimpleNamespace(
             groups=[SimpleNamespace(block_table=table, page_size=page, table_rows=i32([2]))],
-            q_start=i32([0]), q_len=i32([cnt]), kv_len=i32([t0 + cnt]),
-            tiles={tt: (i32([a for a, _ in tiles]), i32([b for _, b in tiles]), len(tiles))})
+            q_start=i32([0]), q_len=i32([cnt]), kv_len=i32([t0 + cnt]), tiles=tiles,
+            decode_only=mode == "runs", max_kv_len=t0 + cnt)
         ctx.q_tiles = lambda size, _c=ctx: _c.tiles[size]
         cache = SimpleNamespace(group=0, k=kc, v=vc)
         out = torch.full((cnt, nq * dv), float("nan"), dtype=torch.bfloat16, device=DEV)
         before = o.launch_count
         o.attention_ext(q[t0:t0 + cnt].reshape(cnt, -1).to(DEV), out, cache, ctx, nq, nkv, d, dv, 0.9,
                         sinks=sinks.float().to(DEV), slopes=slopes.float().to(DEV), values_in_keys=prefix)
-        assert o.launch_count == before + 1 and "attention_rows" in o._configured
+        splits = o._rows_attention_plan(ctx, nq, nkv, d, dv, prefix, torch.device(DEV))[2]
+        assert splits == 1 or mode == "runs"
+        assert o.launch_count == before + (2 if splits > 1 else 1) and "attention_rows" in o._configured
         got.append(out.cpu().double())
         t0 += cnt
     got = torch.cat(got).reshape(n, nq, dv)
