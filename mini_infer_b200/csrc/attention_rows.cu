@@ -47,6 +47,35 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// The CHUNK cache rows listed in rowbase (element offset / width; -1: none, zeros) into shared memory
+// rows of `pitch` elements, their 16-byte pieces un-permuted (piece c of a row at in-page offset t
+// lies at piece c ^ (t & mask)).
+template <int NT>
+__device__ __forceinline__ void gather_rows(bf16* __restrict__ dst, int pitch, const bf16* __restrict__ cache, int width,
+                                            int mask, const int* __restrict__ rowbase, const int* __restrict__ rowoff,
+                                            int tid) {
+  const int pieces = width >> 3, total = CHUNK * pieces;
+  for (int i0 = tid; i0 < total; i0 += 4 * NT) {
+    uint4 v[4];
+    int where[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int idx = i0 + u * NT;
+      v[u] = make_uint4(0, 0, 0, 0);
+      where[u] = -1;
+      if (idx < total) {
+        const int jj = idx / pieces, c = idx - jj * pieces;
+        where[u] = jj * pitch + c * 8;
+        const int base = rowbase[jj];
+        if (base >= 0) v[u] = *reinterpret_cast<const uint4*>(cache + (size_t)base * width + ((c ^ (rowoff[jj] & mask)) << 3));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (where[u] >= 0) *reinterpret_cast<uint4*>(dst + where[u]) = v[u];
+  }
+}
+
 // Which token (within the tile) and which head a row of a tile of R rows stands for.
 struct RowMap {
   int G, R, kvh, hs;
@@ -143,23 +172,9 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
       rowoff[tid] = j % page_size;
     }
     __syncthreads();
-    for (int idx = tid; idx < CHUNK * pieces; idx += NT) {
-      const int jj = idx / pieces, c = idx - jj * pieces;
-      const int base = rowbase[jj];
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (base >= 0) v = *reinterpret_cast<const uint4*>(kcache + (size_t)base * d + ((c ^ (rowoff[jj] & mk)) << 3));
-      *reinterpret_cast<uint4*>(Ks + jj * dp + c * 8) = v;
-    }
-    if (!v_prefix) {
-      const int vpieces = dv >> 3;
-      for (int idx = tid; idx < CHUNK * vpieces; idx += NT) {
-        const int jj = idx / vpieces, c = idx - jj * vpieces;
-        const int base = rowbase[jj];
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (base >= 0) v = *reinterpret_cast<const uint4*>(vcache + (size_t)base * dv + ((c ^ (rowoff[jj] & mv)) << 3));
-        *reinterpret_cast<uint4*>(Vs + jj * dvp + c * 8) = v;
-      }
-    }
+    // four 16-byte pieces per thread are asked for before the first is stored, so that they fly together
+    gather_rows<NT>(Ks, dp, kcache, d, mk, rowbase, rowoff, tid);
+    if (!v_prefix) gather_rows<NT>(Vs, dvp, vcache, dv, mv, rowbase, rowoff, tid);
     __syncthreads();
 
     // ---- S = Q K^T for this warp's 16 keys: two tiles of 8 keys
@@ -311,13 +326,17 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
   }
 }
 
-// Adds up the runs of keys of every row: grid = units x R rows, one block per row.
+// Adds up the runs of keys of every row: grid = units x R rows, one block per row.  The weight of
+// every run (2^(its maximum - the row's maximum)) is worked out once, into shared memory.
+#define MERGE_MAX_SPLITS 64
 __global__ void __launch_bounds__(128)
 attention_rows_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
                             int out_stride, const int* __restrict__ q_start, const int* __restrict__ q_len,
                             const int* __restrict__ tile_req, const int* __restrict__ tile_tok0, int tile_tokens,
                             int nq, int nkv, int dv, const float* __restrict__ sinks, int n_splits, int R) {
   mi_pdl_enter();
+  __shared__ float weight[MERGE_MAX_SPLITS];
+  __shared__ float inv_l;
   constexpr float LOG2E = 1.4426950408889634f;
   const int r = blockIdx.x % R;
   int bid = blockIdx.x / R;
@@ -334,22 +353,37 @@ attention_rows_merge_kernel(const float* __restrict__ part_o, const float* __res
   if (rows.token(r) >= nt) return;
   const int head = rows.head(r);
   const float* pml = part_ml + ((size_t)unit * n_splits * R + r) * 2;
-  float m = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, pml[(size_t)s * R * 2]);
-  float mf = m;
-  if (sinks) mf = fmaxf(m, sinks[head] * LOG2E);
-  float l = sinks ? exp2f(sinks[head] * LOG2E - mf) : 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = pml[(size_t)s * R * 2];
-    if (ms != -INFINITY) l += pml[(size_t)s * R * 2 + 1] * exp2f(ms - mf);
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m = -INFINITY;
+    for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, pml[(size_t)s * R * 2]);
+    m = mi_warp_max(m);
+    const float sink2 = sinks ? sinks[head] * LOG2E : -INFINITY;
+    const float mf = fmaxf(m, sink2);
+    float l = 0.f;
+    for (int s0 = 0; s0 < n_splits; s0 += 32) {     // runs in ascending order: lanes, then the warp's fixed tree
+      const int s = s0 + lane;
+      float w = 0.f, part = 0.f;
+      if (s < n_splits) {
+        const float ms = pml[(size_t)s * R * 2];
+        w = ms == -INFINITY ? 0.f : exp2f(ms - mf);
+        part = pml[(size_t)s * R * 2 + 1] * w;
+        weight[s] = w;
+      }
+      l += mi_warp_sum(part);
+    }
+    if (sinks) l += exp2f(sink2 - mf);
+    if (lane == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
   }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+  __syncthreads();
+  const float inv = inv_l;
   bf16* o = out + (size_t)(q_start[b] + tok0 + rows.token(r)) * out_stride + head * dv;
+  const float* po = part_o + ((size_t)unit * n_splits * R + r) * dv;
   for (int c = threadIdx.x; c < dv; c += blockDim.x) {
     float sum = 0.f;
     for (int s = 0; s < n_splits; ++s) {
-      const float ms = pml[(size_t)s * R * 2];
-      if (ms != -INFINITY) sum += part_o[(((size_t)unit * n_splits + s) * R + r) * dv + c] * exp2f(ms - mf);
+      const float w = weight[s];
+      if (w != 0.f) sum += po[(size_t)s * R * dv + c] * w;
     }
     o[c] = __float2bfloat16_rn(sum * inv);
   }
@@ -395,7 +429,8 @@ extern "C" int mi_attention_rows(const void* q, int q_stride, void* out, int out
     MI_REFUSE("attention_rows: tiles of %d tokens and %d rows do not fit a group of %d heads", tile_tokens, rows, G);
   if (page_size <= 0) MI_REFUSE("attention_rows: bad page size %d", page_size);
   if (!v_prefix && !vcache) MI_REFUSE("attention_rows: no value cache");
-  if (n_splits < 1 || (n_splits > 1 && (!part_o || !part_ml))) MI_REFUSE("attention_rows: several runs of keys need scratch");
+  if (n_splits < 1 || n_splits > MERGE_MAX_SPLITS || (n_splits > 1 && (!part_o || !part_ml)))
+    MI_REFUSE("attention_rows: 1 to %d runs of keys, and scratch for more than one", MERGE_MAX_SPLITS);
   if (!mi_aligned(q, 16) || !mi_aligned(kcache, 16) || !mi_aligned(vcache, 16) || !mi_aligned(out, 4) ||
       !mi_aligned(part_o, 8) || q_stride % 8 || out_stride % 2)
     MI_REFUSE("attention_rows: q and the caches must be 16-byte aligned with rows of whole 16-byte pieces");

@@ -1759,7 +1759,7 @@ def _rows_attention_plan(ctx, nq: int, nkv: int, d: int, dv: int, values_in_keys
     tt = rows_attention_tile_tokens(group, 16)
     units = ctx.tiles[tt][2] * nkv * max(1, group // 16)
     chunks = max(1, -(-int(getattr(ctx, "max_kv_len", 0) or 64) // 64))
-    splits = max(1, min(-(-2 * _sms(device) // units), chunks, 64))
+    splits = max(1, min(-(-4 * _sms(device) // units), chunks, 64))
     return 16, tt, splits
 
 

@@ -19,7 +19,8 @@
 //                           latent's space.
 //                           Rotation, half layout: among the first `rot` of the rot_dim dimensions, i pairs
 //                           with i + rot/2; (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = p * freq[i];
-//                           the angle and its sine and cosine are computed in double precision.
+//                           the angle is computed and reduced to [-pi, pi] in double precision, its sine
+//                           and cosine in fp32.
 #include "common.cuh"
 
 MI_DEFINE_ERROR_API()
@@ -135,10 +136,13 @@ latent_prepare_kernel(const T* __restrict__ packed, int stride, int q_off, int n
   const int half = rot >> 1;
   const double pos = (double)positions[t];
   for (int i = tid; i < half; i += blockDim.x) {
-    double s, c;
-    sincos(pos * freq[i], &s, &c);
-    sn[i] = (float)s;
-    cs[i] = (float)c;
+    // the angle in double precision, brought into [-pi, pi] there; its sine and cosine in fp32
+    double a = pos * freq[i];
+    a -= 6.283185307179586476925 * rint(a * 0.15915494309189533577);
+    float s, c;
+    sincosf((float)a, &s, &c);
+    sn[i] = s;
+    cs[i] = c;
   }
   // the latent's sum of squares (fixed order: by thread, then by warp)
   float ss = 0.f;
