@@ -42,6 +42,11 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, co
   const unsigned s = (unsigned)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(s));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t s) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -179,17 +184,19 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
 
     // ---- S = Q K^T for this warp's 16 keys: two tiles of 8 keys
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    const bf16* qa = Qs + r_lo * dp + 2 * t4;
-    const bf16* kb0 = Ks + (warp * 16 + g) * dp + 2 * t4;
-    const bf16* kb1 = kb0 + 8 * dp;
+    // one ldmatrix.x4 per operand and step of 16 dimensions.  A: lanes 0..15 address rows 0..15 at
+    // dimension k0, lanes 16..31 the same rows at k0 + 8 (matrices a0, a1, a2, a3 in that order).  B: lanes
+    // 0..7 keys 0..7 at k0, 8..15 the same keys at k0 + 8, 16..31 likewise for keys 8..15 (b0, b1 of the
+    // first eight keys, then of the second eight).
+    const uint32_t qaddr = (uint32_t)__cvta_generic_to_shared(Qs + (mt * ROWS + (lane & 15)) * dp + ((lane >> 4) << 3));
+    const uint32_t kaddr = (uint32_t)__cvta_generic_to_shared(
+        Ks + (warp * 16 + ((lane >> 4) << 3) + (lane & 7)) * dp + (((lane >> 3) & 1) << 3));
     for (int k0 = 0; k0 < d; k0 += 16) {
-      uint32_t a[4];
-      a[0] = *reinterpret_cast<const uint32_t*>(qa + k0);
-      a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * dp + k0);
-      a[2] = *reinterpret_cast<const uint32_t*>(qa + k0 + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * dp + k0 + 8);
-      mma_bf16(s[0], a, *reinterpret_cast<const uint32_t*>(kb0 + k0), *reinterpret_cast<const uint32_t*>(kb0 + k0 + 8));
-      mma_bf16(s[1], a, *reinterpret_cast<const uint32_t*>(kb1 + k0), *reinterpret_cast<const uint32_t*>(kb1 + k0 + 8));
+      uint32_t a[4], bfrag[4];
+      ldmatrix_x4(a, qaddr + k0 * 2);
+      ldmatrix_x4(bfrag, kaddr + k0 * 2);
+      mma_bf16(s[0], a, bfrag[0], bfrag[1]);
+      mma_bf16(s[1], a, bfrag[2], bfrag[3]);
     }
     // ---- scale, distance bias, mask; everything in units of log2
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
@@ -379,13 +386,27 @@ attention_rows_merge_kernel(const float* __restrict__ part_o, const float* __res
   const float inv = inv_l;
   bf16* o = out + (size_t)(q_start[b] + tok0 + rows.token(r)) * out_stride + head * dv;
   const float* po = part_o + ((size_t)unit * n_splits * R + r) * dv;
-  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
-    float sum = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float w = weight[s];
-      if (w != 0.f) sum += po[(size_t)s * R * dv + c] * w;
+  // every run has written its sums (zeros where it had no keys), so all of them are read: four columns
+  // per thread, eight runs in flight
+  for (int c = threadIdx.x * 4; c < dv; c += blockDim.x * 4) {
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    int s = 0;
+    for (; s + 8 <= n_splits; s += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const float4*>(po + (size_t)(s + u) * R * dv + c);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float w = weight[s + u];
+        sum.x += v[u].x * w; sum.y += v[u].y * w; sum.z += v[u].z * w; sum.w += v[u].w * w;
+      }
     }
-    o[c] = __float2bfloat16_rn(sum * inv);
+    for (; s < n_splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(po + (size_t)s * R * dv + c);
+      const float w = weight[s];
+      sum.x += v.x * w; sum.y += v.y * w; sum.z += v.z * w; sum.w += v.w * w;
+    }
+    *reinterpret_cast<uint2*>(o + c) = make_uint2(pack_bf16(sum.x * inv, sum.y * inv), pack_bf16(sum.z * inv, sum.w * inv));
   }
 }
 
@@ -432,7 +453,7 @@ extern "C" int mi_attention_rows(const void* q, int q_stride, void* out, int out
   if (n_splits < 1 || n_splits > MERGE_MAX_SPLITS || (n_splits > 1 && (!part_o || !part_ml)))
     MI_REFUSE("attention_rows: 1 to %d runs of keys, and scratch for more than one", MERGE_MAX_SPLITS);
   if (!mi_aligned(q, 16) || !mi_aligned(kcache, 16) || !mi_aligned(vcache, 16) || !mi_aligned(out, 4) ||
-      !mi_aligned(part_o, 8) || q_stride % 8 || out_stride % 2)
+      !mi_aligned(part_o, 16) || q_stride % 8 || out_stride % 2 || (n_splits > 1 && (!mi_aligned(out, 8) || out_stride % 4)))
     MI_REFUSE("attention_rows: q and the caches must be 16-byte aligned with rows of whole 16-byte pieces");
   const long long units = (long long)n_tiles * nkv * (G >= rows ? G / rows : 1);
   const long long blocks = units * n_splits;

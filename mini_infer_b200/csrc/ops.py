@@ -1790,7 +1790,7 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
         raise KernelError("attention: the value cache must be contiguous [pages, nkv, page_size, dv] in q's dtype")
     bt = group.block_table
     if (q.dtype == torch.bfloat16 and not window and rows_attention_supported(nq, nkv, d, dv, values_in_keys)
-            and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
+            and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0
             and rows_attention_tile_tokens(nq // nkv, 16) in ctx.tiles):
         rows, tt, splits = _rows_attention_plan(ctx, nq, nkv, d, dv, values_in_keys, q.device)
         tile_req, tile_tok0, n_tiles = ctx.q_tiles(tt)

@@ -1,5 +1,6 @@
 // What stands between an attention's input projection and the attention itself, for two kinds
-// of attention.  Both kernels take one block per token and read column ranges of one packed
+// of attention.  Both kernels take the tokens one by one (a block, or a few blocks that share the
+// heads, per token) and read column ranges of one packed
 // projection [tokens, stride]; norms, angles, sines and cosines are fp32 or better, every value
 // is rounded once.
 //
@@ -43,7 +44,8 @@ qk_bias_norm_store_kernel(T* __restrict__ packed, int stride, int q_off, int k_o
   const int page = slot / page_size, offset = slot - page * page_size;
   const int mk = mi_swizzle_mask_rows(d, (int)sizeof(T)), mv = mi_swizzle_mask_rows(dv, (int)sizeof(T));
   const int n_heads = nq + nkv + (values_are_keys ? 0 : nkv);
-  for (int h = warp; h < n_heads; h += nwarps) {
+  // a block's warps take the heads blockIdx.y * warps .. : all heads of a token at once
+  for (int h = blockIdx.y * nwarps + warp; h < n_heads; h += gridDim.y * nwarps) {
     if (h >= nq + nkv) {              // values with columns of their own
       if (!writes) continue;
       const int kvh = h - nq - nkv;
@@ -106,12 +108,14 @@ extern "C" int mi_qk_bias_norm_store(void* packed, int stride, int q_off, int k_
   if (d <= 0 || d > 32 * QK_MAX_PER_LANE || dv <= 0) MI_REFUSE("qk_prepare: head size %d must lie in [1, %d]", d, 32 * QK_MAX_PER_LANE);
   if (values_are_keys && dv != d) MI_REFUSE("qk_prepare: values that are the keys have the keys' size, not %d", dv);
   if (writes && (!slots || !kcache || !vcache || page_size <= 0)) MI_REFUSE("qk_prepare: a cache write needs slots and pages");
+  const int n_heads = nq + nkv + (values_are_keys ? 0 : nkv);
+  const dim3 grid((unsigned)M, (unsigned)((n_heads + 3) / 4 < 64 ? (n_heads + 3) / 4 : 64));
   if (dtype == MI_DTYPE_F32)
-    MI_LAUNCH((qk_bias_norm_store_kernel<float>), M, 128, 0, stream, (float*)packed, stride, q_off, k_off, v_off, nq, nkv,
+    MI_LAUNCH((qk_bias_norm_store_kernel<float>), grid, 128, 0, stream, (float*)packed, stride, q_off, k_off, v_off, nq, nkv,
               d, dv, q_bias, k_bias, q_gain, k_gain, eps, values_are_keys, slots, (float*)kcache, (float*)vcache,
               page_size, writes);
   else if (dtype == MI_DTYPE_BF16)
-    MI_LAUNCH((qk_bias_norm_store_kernel<bf16>), M, 128, 0, stream, (bf16*)packed, stride, q_off, k_off, v_off, nq, nkv,
+    MI_LAUNCH((qk_bias_norm_store_kernel<bf16>), grid, 128, 0, stream, (bf16*)packed, stride, q_off, k_off, v_off, nq, nkv,
               d, dv, q_bias, k_bias, q_gain, k_gain, eps, values_are_keys, slots, (bf16*)kcache, (bf16*)vcache,
               page_size, writes);
   else
