@@ -261,7 +261,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ q_start, const int* __restrict__ q_len,
                             const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                             const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale, int window,
-                            int gb, int tt) {
+                            int gb, int tt, const float* __restrict__ sinks, const float* __restrict__ slopes) {
   mi_pdl_enter();   // inputs come from the kernels before this one
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -452,6 +452,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tmem_o = tmem + TM_O + t * 128;
     const float sc = scale * LOG2E;
+    // optional extras, per head: a distance bias (the scaled score of a key `dist` positions back is
+    // lowered by slope * dist: taken off the raw scores, in their units) and a sink (a score without a
+    // key that joins the denominator once)
+    const int head = kvh * g + hb * gb + mem;
+    const float bias_per_step = (slopes && rvalid) ? slopes[head] / scale : 0.f;
+    const float sink2 = (sinks && rvalid) ? sinks[head] * LOG2E : -INFINITY;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int it = 0; it < n_chunks; ++it) {
@@ -470,6 +476,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           s[i] = __uint_as_float(ra[i]);
           s[32 + i] = __uint_as_float(rb[i]);
         }
+      }
+      if (slopes) {   // (the same for the whole block)
+        const float back = (float)(prow - key0);
+#pragma unroll
+        for (int j = 0; j < 64; ++j) s[j] = fmaf(bias_per_step, (float)j - back, s[j]);
       }
       const bool interior = key0 + KC - 1 <= t_first && key0 >= (window > 0 ? max(0, t_last - window + 1) : 0) && key0 >= lo;
       if (!interior || !rvalid) {
@@ -576,6 +587,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // the output: O / l
     if (ok && n_chunks > 0 && warp_wait(&bars[B_PVDONE + 2 * t + ((n_chunks - 1) & 1)], ((n_chunks - 1) >> 1) & 1, gu)) {
       tc_fence_after();
+      if (sinks && rvalid && m_run != -INFINITY) l_run += fast_exp2(sink2 - m_run);   // the exponents' reference is m_run
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       bf16* orow = out + (size_t)(qs + tok0 + tk) * out_stride + (size_t)(kvh * g + hb * gb + mem) * d;
       for (int c32 = 0; c32 < d; c32 += 32) {
@@ -675,11 +687,15 @@ extern "C" int mi_attention_prefill_tc_tile_tokens(int g) {
 
 // Same arguments as mi_attention_prefill (attention_mma.cu) plus the number of pages of the
 // cache; tiles are mi_attention_prefill_tc_tile_tokens(g) tokens.
-extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
-                                       const void* vcache, long long n_pages, const int* block_table, int bt_stride,
-                                       const int* table_rows, int page_size, const int* q_start, const int* q_len, const int* kv_len,
-                                       const int* tile_req, const int* tile_tok0, int n_tiles, int tile_tokens,
-                                       int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+// `sinks` / `slopes` (fp32 [nq], either may be null): a score per head that joins the softmax's
+// denominator without a key or a value, and a distance bias (the scaled score of a key `dist`
+// positions back is lowered by slopes[h] * dist).
+extern "C" int mi_attention_prefill_tc_ext(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
+                                           const void* vcache, long long n_pages, const int* block_table, int bt_stride,
+                                           const int* table_rows, int page_size, const int* q_start, const int* q_len,
+                                           const int* kv_len, const int* tile_req, const int* tile_tok0, int n_tiles,
+                                           int tile_tokens, int nq, int nkv, int d, float scale, int window,
+                                           const float* sinks, const float* slopes, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (!mi_attention_prefill_tc_supported(nq, nkv, d, page_size))
     MI_REFUSE("attention_tc: sizes not taken (heads %d/%d, head size %d, pages of %d)", nq, nkv, d, page_size);
@@ -709,6 +725,16 @@ extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, i
   dim3 grid((unsigned)n_blocks);
   MI_LAUNCH((kern), grid, TC_THREADS, smem, stream, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride,
             block_table, bt_stride, table_rows, page_size, page_shift, q_start, q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, scale,
-            window, gb, NTILE * ROWS / gb);
+            window, gb, NTILE * ROWS / gb, sinks, slopes);
   MI_RETURN_LAUNCH_STATUS();
+}
+
+extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
+                                       const void* vcache, long long n_pages, const int* block_table, int bt_stride,
+                                       const int* table_rows, int page_size, const int* q_start, const int* q_len, const int* kv_len,
+                                       const int* tile_req, const int* tile_tok0, int n_tiles, int tile_tokens,
+                                       int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+  return mi_attention_prefill_tc_ext(q, q_stride, out, out_stride, kcache, vcache, n_pages, block_table, bt_stride,
+                                     table_rows, page_size, q_start, q_len, kv_len, tile_req, tile_tok0, n_tiles,
+                                     tile_tokens, nq, nkv, d, scale, window, nullptr, nullptr, stream);
 }

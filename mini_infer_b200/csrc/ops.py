@@ -203,6 +203,10 @@ def _sig_attention_tc(lib: ctypes.CDLL) -> None:
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
         c_void_p]
+    lib.mi_attention_prefill_tc_ext.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+        c_void_p, c_void_p, c_void_p]
     lib.mi_attention_prefill_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
     lib.mi_attention_tc_status.argtypes = [c_int]
     lib.mi_set_status_word.argtypes = [c_void_p]
@@ -792,10 +796,16 @@ def prefill_tc_supported(nq: int, nkv: int, head_dim: int, page_size: int) -> bo
 
 def attention_prefill_tc(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, q_len, kv_len,
                          tile_req, tile_tok0, n_tiles, tile_tokens, nq, nkv, head_dim, scale, window=0,
-                         table_rows=None) -> None:
+                         table_rows=None, sinks: torch.Tensor | None = None,
+                         slopes: torch.Tensor | None = None) -> None:
     """bfloat16 attention of query portions over the paged cache on tcgen05 (attention_tc.cu);
-    same arguments as ``attention_prefill``."""
-    _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0, table_rows)
+    same arguments as ``attention_prefill``, and optionally ``sinks`` / ``slopes`` (fp32 ``[nq]``: a
+    score per head in the softmax's denominator without a key; a distance bias ``slope * (i - j)``
+    taken off the scaled scores)."""
+    _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0, table_rows, sinks, slopes)
+    for name, t in (("sinks", sinks), ("slopes", slopes)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != nq or not t.is_contiguous()):
+            raise KernelError(f"attention_prefill_tc: {name} must be contiguous fp32 [{nq}]")
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill_tc: bfloat16 only")
     _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size,
@@ -803,11 +813,11 @@ def attention_prefill_tc(q, q_stride, out, kcache, vcache, block_table, page_siz
                            ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0),
                            ("table_rows", table_rows)))
     lib = _waiting_lib("attention_tc", q.device)
-    rc = lib.mi_attention_prefill_tc(
+    rc = lib.mi_attention_prefill_tc_ext(
         _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), int(kcache.shape[0]),
         _ptr(block_table), block_table.stride(0), _ptr(table_rows), int(page_size), _ptr(q_start), _ptr(q_len), _ptr(kv_len),
         _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), int(tile_tokens), nq, nkv, head_dim, float(scale),
-        int(window), _stream())
+        int(window), _ptr(sinks), _ptr(slopes), _stream())
     _finish(lib, rc, "attention_prefill_tc")
 
 
@@ -1770,7 +1780,8 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
     head that joins the softmax's denominator without a key or a value), ``slopes`` (fp32 ``[nq]``:
     the scaled score of a key ``dist`` positions back is lowered by ``slope * dist``) and
     ``values_in_keys`` (the cache layer has keys only; a key's value is the first ``dv`` numbers of its
-    own row).  fp32 scores, weights and sums for float32 and bfloat16 alike.  bfloat16 with sizes that
+    own row).  fp32 scores, weights and sums for float32 and bfloat16 alike.  bfloat16 prompt portions
+    with keys and values of one size that attention_tc.cu takes run on tcgen05; other bfloat16 steps with sizes that
     attention_rows.cu takes (``rows_attention_supported``) and tiles planned for it runs on tensor
     cores (weights rounded to bfloat16 for the second product); everything else on CUDA cores."""
     global launch_count
@@ -1789,6 +1800,18 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
                            or not vc.is_contiguous()):
         raise KernelError("attention: the value cache must be contiguous [pages, nkv, page_size, dv] in q's dtype")
     bt = group.block_table
+    # prompt portions of heads that the tcgen05 prefill kernel takes (keys and values of 64 or 128) go there
+    if (q.dtype == torch.bfloat16 and not values_in_keys and d == dv and not getattr(ctx, "decode_only", False)
+            and USE_TC_PREFILL and scale > 0 and prefill_tc_supported(nq, nkv, d, group.page_size)
+            and prefill_tc_tile_tokens(nq // nkv) in ctx.tiles and out.is_contiguous()
+            and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
+            and kc.data_ptr() % 128 == 0 and vc.data_ptr() % 128 == 0):
+        tt = prefill_tc_tile_tokens(nq // nkv)
+        tile_req, tile_tok0, n_tiles = ctx.q_tiles(tt)
+        attention_prefill_tc(q, q.stride(0), out, kc, vc, bt, group.page_size, ctx.q_start, ctx.q_len, ctx.kv_len,
+                             tile_req, tile_tok0, n_tiles, tt, nq, nkv, d, scale, int(window),
+                             table_rows=group.table_rows, sinks=sinks, slopes=slopes)
+        return
     if (q.dtype == torch.bfloat16 and not window and rows_attention_supported(nq, nkv, d, dv, values_in_keys)
             and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0
             and rows_attention_tile_tokens(nq // nkv, 16) in ctx.tiles):

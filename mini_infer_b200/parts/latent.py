@@ -202,6 +202,8 @@ class DistanceBiasAttention(ProjectedMixer):
 
     def plan_needs(self):
         tiles = {ops.ATTENTION_TILE_TOKENS} | ops.rows_attention_tile_sizes(self.nq, self.nkv, self.d, self.dv, False)
+        if self.d == self.dv and self.d in (64, 128):      # sizes the tcgen05 prefill kernel takes
+            tiles.add(ops.prefill_tc_tile_tokens(self.nq // self.nkv))
         return PlanNeeds(frozenset(tiles))
 
     def bind(self, tensors, dtype, device):

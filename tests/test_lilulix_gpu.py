@@ -319,7 +319,7 @@ def test_latent_rows_and_rotated_query_parts(n, d, rd, rot, rank):
     assert torch.isnan(qfull[:, :, :rank]).all()                     # the caller fills the latent part
 
 
-def attention_fixture(nq, nkv, d, n_tokens, page, portions, latent_rank=0):
+def attention_fixture(nq, nkv, d, n_tokens, page, portions, latent_rank=0, dtype="float32"):
     """A runner with one attention layer, a request fed in ``portions``, and per portion the step's
     context and the layer's cache, so that a test can put rows of its own into the pages."""
     from mini_infer_b200.engine import ModelRunner
@@ -331,7 +331,7 @@ def attention_fixture(nq, nkv, d, n_tokens, page, portions, latent_rank=0):
     else:
         layer = biased(heads=nq, kv_heads=nkv, dim=d, scale=1.0, ff=None)
     cfg = config([layer], vocab=8, width=16, eps=1e-6, buckets=3, mul_prev=1, mul_cur=1, loop=None)
-    runner = ModelRunner.from_state_dict(cfg, random_state(cfg, seed=3), dtype="float32", block_size=page,
+    runner = ModelRunner.from_state_dict(cfg, random_state(cfg, seed=3), dtype=dtype, block_size=page,
                                          num_blocks=-(-n_tokens // page) + 1, max_requests=2)
     for st in runner.cache.storage:
         st.fill_(float("nan"))
@@ -523,3 +523,50 @@ def test_tensor_core_attention_against_the_plain_softmax(nq, nkv, d, dv, prefix,
     late = got[n - 20:, 0]
     target = k.double()[marked, 0, :dv] if prefix else torch.full((dv,), 3.0, dtype=torch.float64)
     assert (late - target).abs().max() <= 2e-2 * max(1.0, target.abs().max())
+
+
+@pytest.mark.parametrize("nq,nkv,d", [(8, 2, 128), (4, 4, 64), (16, 1, 64)])
+@pytest.mark.parametrize("portions,page", [((333,), 16), ((3, 130, 2, 70, 1, 1, 40), 8)])
+def test_prompt_portions_on_the_tcgen05_kernel_with_sinks_and_slopes(nq, nkv, d, portions, page):
+    """bfloat16 heads of 64 and 128 whose values have the keys' size: prompt portions run on the tcgen05
+    prefill kernel, single tokens on the kernel of rows, both with the distance bias and the sink; one
+    key stands out far back at a page's last slot."""
+    from mini_infer_b200.engine import StepEntry
+
+    n = sum(portions)
+    runner = attention_fixture(nq, nkv, d, n, page, portions, dtype="bfloat16")
+    o = ops()
+    q = rnd(n, nq, d, seed=1, scale=d ** -0.25).bfloat16()
+    k = rnd(n, nkv, d, seed=2, scale=d ** -0.25).bfloat16()
+    marked = page - 1
+    k[marked] = 0.0
+    k[marked, :, d - 1] = 6.0
+    q[n - 20:, 0] = 0.0
+    q[n - 20:, 0, d - 1] = 5.0
+    slopes = torch.linspace(0.0, 0.2, nq, dtype=torch.float64)
+    sinks = torch.linspace(-3.0, 3.0, nq, dtype=torch.float64)
+    want = plain_scores_attention(q.double(), k.double(), k.double(), 0.9, slopes, sinks)
+    got, t0, used_tc = [], 0, False
+    for cnt in portions:
+        ctx, caches, _, _ = runner.stepper.plan([StepEntry("a", [0] * cnt, [])])
+        runner.stepper.apply_table_updates(ctx)
+        cache = caches[0]
+        packed = torch.cat([q[t0:t0 + cnt].reshape(cnt, -1), k[t0:t0 + cnt].reshape(cnt, -1)], dim=1).to(DEV)
+        o.qk_bias_norm_store(packed, 0, nq * d, 0, nq, nkv, d, d, q_bias=None, k_bias=None, q_gain=None, k_gain=None,
+                             eps=0.0, values_are_keys=True, slots=ctx.groups[cache.group].slots, kcache=cache.k,
+                             vcache=cache.v)
+        out = torch.full((cnt, nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        before = set(o._configured)
+        o.attention_ext(packed[:, :nq * d], out, cache, ctx, nq, nkv, d, d, 0.9, sinks=sinks.float().to(DEV),
+                        slopes=slopes.float().to(DEV))
+        if cnt > 1:
+            used_tc = used_tc or "attention_tc" in o._configured
+        else:
+            assert "attention_rows" in o._configured
+        got.append(out.cpu().double())
+        t0 += cnt
+    assert used_tc and o.attention_tc_status() == 0
+    got = torch.cat(got).reshape(n, nq, d)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() <= 2e-2 * max(1.0, want.abs().max())
+    assert (got[n - 20:, 0] - k.double()[marked, 0]).abs().max() <= 2e-2 * 6.0
