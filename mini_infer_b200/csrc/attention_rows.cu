@@ -5,7 +5,8 @@
 // head.  Prompt portions and single decoded tokens alike.
 //
 // A block takes R = 16 MT query rows that share one key/value head (MT = 1: four warps, for steps of
-// single tokens; MT = 4: sixteen warps, for prompt portions): with G = nq / nkv query heads per
+// single tokens; MT = 2 or 4: eight or sixteen warps, for prompt portions, with two buffers for the
+// chunk's rows where shared memory allows, so that the next chunk is copied while this one is multiplied): with G = nq / nkv query heads per
 // key/value head, the rows are (token, head in group) pairs, R / G tokens by G heads when G divides
 // R, or R of the G heads of one token when R divides G.  It walks the request's keys in chunks of 64
 // (cut at absolute multiples of 64): the chunk's rows are gathered from their pages into shared
@@ -81,6 +82,24 @@ __device__ __forceinline__ void gather_rows(bf16* __restrict__ dst, int pitch, c
   }
 }
 
+// The same gather as asynchronous copies (cp.async, 16 bytes each; a row that is not there is filled
+// with zeros by a copy of no bytes): the caller commits the group and waits for it later.
+template <int NT>
+__device__ __forceinline__ void gather_rows_async(bf16* __restrict__ dst, int pitch, const bf16* __restrict__ cache,
+                                                  int width, int mask, const int* __restrict__ rowbase,
+                                                  const int* __restrict__ rowoff, int tid) {
+  const int pieces = width >> 3, total = CHUNK * pieces;
+  for (int idx = tid; idx < total; idx += NT) {
+    const int jj = idx / pieces, c = idx - jj * pieces;
+    const int base = rowbase[jj];
+    const bf16* src = base >= 0 ? cache + (size_t)base * width + ((c ^ (rowoff[jj] & mask)) << 3) : cache;
+    const unsigned to = (unsigned)__cvta_generic_to_shared(dst + jj * pitch + c * 8);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(to), "l"(src), "r"(base >= 0 ? 16 : 0) : "memory");
+  }
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
 // Which token (within the tile) and which head a row of a tile of R rows stands for.
 struct RowMap {
   int G, R, kvh, hs;
@@ -88,8 +107,9 @@ struct RowMap {
   __device__ __forceinline__ int head(int r) const { return G >= R ? kvh * G + hs * R + r : kvh * G + r % G; }
 };
 
-// DVW: value columns per warp that the accumulators have room for (dv <= 4 * DVW).
-template <int DVW, int MT>
+// DVW: value columns per warp that the accumulators have room for (dv <= 4 * DVW).  DB: two buffers for
+// the chunk's rows; the next chunk is copied (cp.async) while this one is multiplied.
+template <int DVW, int MT, bool DB>
 __global__ void __launch_bounds__(QUARTERS * MT * 32)
 attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                       const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
@@ -103,14 +123,15 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
   constexpr int R = ROWS * MT, NW = QUARTERS * MT, NT = NW * 32;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int dp = d + PAD, dvp = dv + PAD;
+  constexpr int STAGES = DB ? 2 : 1;
+  const int stage_elems = CHUNK * dp + (v_prefix ? 0 : CHUNK * dvp);   // a chunk's keys [CHUNK][dp], then its values [CHUNK][dvp]
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [R][dp]
-  bf16* Ks = Qs + R * dp;                                       // [CHUNK][dp]
-  bf16* Vs = Ks + CHUNK * dp;                                   // [CHUNK][dvp] (nothing with v_prefix)
-  bf16* Ps = v_prefix ? Vs : Vs + CHUNK * dvp;                  // [R][CHUNK + PAD]
+  bf16* KV = Qs + R * dp;                                       // [STAGES][stage_elems]
+  bf16* Ps = KV + STAGES * stage_elems;                         // [R][CHUNK + PAD]
   float* wmax = reinterpret_cast<float*>(Ps + R * (CHUNK + PAD));      // [QUARTERS][R]
   float* wsum = wmax + QUARTERS * R;                            // [QUARTERS][R]
-  int* rowbase = reinterpret_cast<int*>(wsum + QUARTERS * R);   // [CHUNK] cache row of each key, -1: none
-  int* rowoff = rowbase + CHUNK;                                // [CHUNK] in-page offset of each key
+  int* rowbase_all = reinterpret_cast<int*>(wsum + QUARTERS * R);      // [STAGES][CHUNK] cache row of each key, -1: none
+  int* rowoff_all = rowbase_all + STAGES * CHUNK;               // [STAGES][CHUNK] in-page offset of each key
 
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = (tid >> 5) % QUARTERS, mt = (tid >> 5) / QUARTERS;   // the quarter, and which 16 rows
@@ -161,26 +182,54 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict
   const int col0 = warp * (dv / QUARTERS);                      // this warp's value columns
   const int ntiles_v = (dv / QUARTERS) >> 3;
   const int mk = mi_swizzle_mask_rows(d, 2), mv = mi_swizzle_mask_rows(dv, 2);
-  const bf16* Vrows = v_prefix ? Ks : Vs;
   const int vpitch = v_prefix ? dp : dvp;
-
-  for (int j0 = j_begin; j0 < j_stop; j0 += CHUNK) {
-    __syncthreads();                                            // the chunk before is consumed (first time: Qs written)
+  // where the 64 keys from j0 on lie in the cache (threads 0..63), into list `which`
+  auto list_rows = [&](int j0, int which) {
     if (tid < CHUNK) {
       const int j = j0 + tid;
       int base = -1;
-      if (j < j_end) {
+      if (j < j_stop) {
         const int page = block_table[(size_t)trow * bt_stride + j / page_size];
         base = (page * nkv + kvh) * page_size + j % page_size;
       }
-      rowbase[tid] = base;
-      rowoff[tid] = j % page_size;
+      rowbase_all[which * CHUNK + tid] = base;
+      rowoff_all[which * CHUNK + tid] = j % page_size;
     }
+  };
+  auto copy_chunk = [&](int which) {     // asynchronous copies of the chunk listed in `which` into buffer `which`
+    bf16* kdst = KV + which * stage_elems;
+    gather_rows_async<NT>(kdst, dp, kcache, d, mk, rowbase_all + which * CHUNK, rowoff_all + which * CHUNK, tid);
+    if (!v_prefix)
+      gather_rows_async<NT>(kdst + CHUNK * dp, dvp, vcache, dv, mv, rowbase_all + which * CHUNK, rowoff_all + which * CHUNK, tid);
+    cp_async_commit();
+  };
+  if (DB && j_begin < j_stop) {
+    list_rows(j_begin, 0);
     __syncthreads();
-    // four 16-byte pieces per thread are asked for before the first is stored, so that they fly together
-    gather_rows<NT>(Ks, dp, kcache, d, mk, rowbase, rowoff, tid);
-    if (!v_prefix) gather_rows<NT>(Vs, dvp, vcache, dv, mv, rowbase, rowoff, tid);
-    __syncthreads();
+    copy_chunk(0);
+    list_rows(j_begin + CHUNK, 1);
+  }
+
+  int it = 0;
+  for (int j0 = j_begin; j0 < j_stop; j0 += CHUNK, ++it) {
+    const int cur = DB ? (it & 1) : 0;
+    const bf16* Ks = KV + cur * stage_elems;
+    const bf16* Vrows = v_prefix ? Ks : Ks + CHUNK * dp;
+    if (DB) {
+      cp_async_wait_all();
+      __syncthreads();          // this chunk has landed, the next one's rows are listed, the chunk before is consumed
+      if (j0 + CHUNK < j_stop) copy_chunk(cur ^ 1);
+      list_rows(j0 + 2 * CHUNK, cur);      // read after the next iteration's barrier (this chunk's list has done its work)
+    } else {
+      __syncthreads();                                          // the chunk before is consumed (first time: Qs written)
+      list_rows(j0, 0);
+      __syncthreads();
+      // four 16-byte pieces per thread are asked for before the first is stored, so that they fly together
+      bf16* kdst = KV;
+      gather_rows<NT>(kdst, dp, kcache, d, mk, rowbase_all, rowoff_all, tid);
+      if (!v_prefix) gather_rows<NT>(kdst + CHUNK * dp, dvp, vcache, dv, mv, rowbase_all, rowoff_all, tid);
+      __syncthreads();
+    }
 
     // ---- S = Q K^T for this warp's 16 keys: two tiles of 8 keys
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -413,7 +462,7 @@ attention_rows_merge_kernel(const float* __restrict__ part_o, const float* __res
 // Tokens per tile of `rows` rows for a group of G query heads per key/value head, or 0 when the
 // kernel does not take the group size.
 extern "C" int mi_attention_rows_tile_tokens(int G, int rows) {
-  if (G <= 0 || (rows != ROWS && rows != 4 * ROWS)) return 0;
+  if (G <= 0 || (rows != ROWS && rows != 2 * ROWS && rows != 4 * ROWS)) return 0;
   if (G >= rows) return G % rows == 0 ? 1 : 0;
   return rows % G == 0 ? rows / G : 0;
 }
@@ -441,8 +490,12 @@ extern "C" int mi_attention_rows(const void* q, int q_stride, void* out, int out
                                  int page_size, const int* q_start, const int* q_len, const int* kv_len,
                                  const int* tile_req, const int* tile_tok0, int n_tiles, int tile_tokens, int rows,
                                  int nq, int nkv, int d, int dv, float scale, const float* sinks, const float* slopes,
-                                 int v_prefix, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                                 int v_prefix, int n_splits, float* part_o, float* part_ml, int stages,
+                                 cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (stages != 1 && stages != 2) MI_REFUSE("attention_rows: one or two buffers for a chunk, not %d", stages);
+  if ((rows == 2 * ROWS && stages != 2) || (rows == ROWS && stages != 1))
+    MI_REFUSE("attention_rows: blocks of %d rows with %d buffers are not built", rows, stages);
   if (!mi_attention_rows_supported(nq, nkv, d, dv, v_prefix))
     MI_REFUSE("attention_rows: sizes not taken (heads %d over %d, keys %d, values %d)", nq, nkv, d, dv);
   const int G = nq / nkv;
@@ -458,13 +511,14 @@ extern "C" int mi_attention_rows(const void* q, int q_stride, void* out, int out
   const long long units = (long long)n_tiles * nkv * (G >= rows ? G / rows : 1);
   const long long blocks = units * n_splits;
   if (blocks > 0x7fffffffLL || units * rows > 0x7fffffffLL) MI_REFUSE("attention_rows: too many blocks for one launch");
-  const size_t smem = ((size_t)(rows + CHUNK) * (d + PAD) + (v_prefix ? 0 : (size_t)CHUNK * (dv + PAD)) +
+  const size_t smem = ((size_t)rows * (d + PAD) +
+                       (size_t)stages * ((size_t)CHUNK * (d + PAD) + (v_prefix ? 0 : (size_t)CHUNK * (dv + PAD))) +
                        (size_t)rows * (CHUNK + PAD)) * sizeof(bf16) +
-                      2 * QUARTERS * rows * sizeof(float) + 2 * CHUNK * sizeof(int);
+                      2 * QUARTERS * rows * sizeof(float) + (size_t)stages * 2 * CHUNK * sizeof(int);
   if (smem > 227 * 1024) MI_REFUSE("attention_rows: keys of %d and values of %d do not fit in shared memory", d, dv);
-#define MI_GO(DVW, MT)                                                                                          \
+#define MI_GO(DVW, MT, DB)                                                                                      \
   do {                                                                                                          \
-    auto kern = attention_rows_kernel<DVW, MT>;                                                                 \
+    auto kern = attention_rows_kernel<DVW, MT, DB>;                                                             \
     if (smem > 48 * 1024) {                                                                                     \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
       if (e != cudaSuccess) return (int)e;                                                                      \
@@ -475,13 +529,21 @@ extern "C" int mi_attention_rows(const void* q, int q_stride, void* out, int out
               v_prefix, n_splits, part_o, part_ml);                                                             \
   } while (0)
   if (rows == ROWS) {
-    if (dv <= 128) MI_GO(32, 1);
-    else if (dv <= 256) MI_GO(64, 1);
-    else MI_GO(128, 1);
+    if (dv <= 128) MI_GO(32, 1, false);
+    else if (dv <= 256) MI_GO(64, 1, false);
+    else MI_GO(128, 1, false);
+  } else if (rows == 2 * ROWS) {
+    if (dv <= 128) MI_GO(32, 2, true);
+    else if (dv <= 256) MI_GO(64, 2, true);
+    else MI_GO(128, 2, true);
+  } else if (stages == 2) {
+    if (dv <= 128) MI_GO(32, 4, true);
+    else if (dv <= 256) MI_GO(64, 4, true);
+    else MI_GO(128, 4, true);
   } else {
-    if (dv <= 128) MI_GO(32, 4);
-    else if (dv <= 256) MI_GO(64, 4);
-    else MI_GO(128, 4);
+    if (dv <= 128) MI_GO(32, 4, false);
+    else if (dv <= 256) MI_GO(64, 4, false);
+    else MI_GO(128, 4, false);
   }
 #undef MI_GO
   {

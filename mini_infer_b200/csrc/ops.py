@@ -287,7 +287,7 @@ def _sig_attention_rows(lib: ctypes.CDLL) -> None:
     lib.mi_attention_rows.argtypes = [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-        c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]
+        c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
     lib.mi_attention_rows_tile_tokens.argtypes = [c_int, c_int]
     lib.mi_attention_rows_supported.argtypes = [c_int, c_int, c_int, c_int, c_int]
 
@@ -1717,7 +1717,7 @@ def latent_prepare(packed: torch.Tensor, q_off: int, nq: int, q_head: int, q_rot
 
 
 USE_ROWS_ATTENTION = os.environ.get("MINI_INFER_ROWS_ATTENTION", "1") != "0"
-ROWS_ATTENTION_ROWS = (16, 64)   # query rows per block of attention_rows.cu: steps of single tokens, prompt portions
+ROWS_ATTENTION_ROWS = (16, 32, 64)   # query rows per block of attention_rows.cu: steps of single tokens; prompt portions
 
 
 def rows_attention_tile_tokens(group: int, rows: int = 16) -> int:
@@ -1752,25 +1752,31 @@ def rows_attention_supported(nq: int, nkv: int, d: int, dv: int, values_in_keys:
     return _rows_attention_smem(16, d, dv, values_in_keys) <= 227 * 1024
 
 
-def _rows_attention_smem(rows: int, d: int, dv: int, values_in_keys: bool) -> int:
-    return ((rows + 64) * (d + 8) + (0 if values_in_keys else 64 * (dv + 8)) + rows * 72) * 2 + 32 * rows + 512
+def _rows_attention_smem(rows: int, d: int, dv: int, values_in_keys: bool, stages: int = 1) -> int:
+    chunk = 64 * (d + 8) + (0 if values_in_keys else 64 * (dv + 8))
+    return (rows * (d + 8) + stages * chunk + rows * 72) * 2 + 32 * rows + stages * 512
 
 
-def _rows_attention_plan(ctx, nq: int, nkv: int, d: int, dv: int, values_in_keys: bool, device) -> tuple[int, int, int]:
-    """``(rows per block, tokens per tile, runs of keys per tile)`` for this step: steps of single
-    tokens take 16 rows and cut every request's keys into runs, so that the blocks fill the GPU;
-    prompt portions take 64 rows where the group size and shared memory allow."""
+def _rows_attention_plan(ctx, nq: int, nkv: int, d: int, dv: int, values_in_keys: bool, device) -> tuple[int, int, int, int]:
+    """``(rows per block, tokens per tile, runs of keys per tile, buffers per chunk)`` for this step:
+    steps of single tokens take 16 rows and cut every request's keys into runs, so that the blocks
+    fill the GPU; prompt portions take 64 rows with two buffers for the chunk's rows (the next chunk
+    is copied while this one is multiplied), else 64 rows with one buffer, else 32 rows with two, as
+    the group size and shared memory allow."""
     group = nq // nkv
     if not getattr(ctx, "decode_only", False):
-        tt = rows_attention_tile_tokens(group, 64)
-        if tt and tt in ctx.tiles and _rows_attention_smem(64, d, dv, values_in_keys) <= 227 * 1024:
-            return 64, tt, 1
-        return 16, rows_attention_tile_tokens(group, 16), 1
+        # measured at 2048 tokens: two buffers gain 13 % at 64 rows; 32 rows with two buffers lose 30 % against 64
+        # rows with one for rows of 576 (twice the traffic from the L2) and tie for rows of 160 and less
+        for rows, stages in ((64, 2), (64, 1), (32, 2)):
+            tt = rows_attention_tile_tokens(group, rows)
+            if tt and tt in ctx.tiles and _rows_attention_smem(rows, d, dv, values_in_keys, stages) <= 227 * 1024:
+                return rows, tt, 1, stages
+        return 16, rows_attention_tile_tokens(group, 16), 1, 1
     tt = rows_attention_tile_tokens(group, 16)
     units = ctx.tiles[tt][2] * nkv * max(1, group // 16)
     chunks = max(1, -(-int(getattr(ctx, "max_kv_len", 0) or 64) // 64))
     splits = max(1, min(-(-4 * _sms(device) // units), chunks, 64))
-    return 16, tt, splits
+    return 16, tt, splits, 1
 
 
 def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: int, d: int, dv: int, scale: float, *,
@@ -1815,7 +1821,7 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
     if (q.dtype == torch.bfloat16 and not window and rows_attention_supported(nq, nkv, d, dv, values_in_keys)
             and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0
             and rows_attention_tile_tokens(nq // nkv, 16) in ctx.tiles):
-        rows, tt, splits = _rows_attention_plan(ctx, nq, nkv, d, dv, values_in_keys, q.device)
+        rows, tt, splits, stages = _rows_attention_plan(ctx, nq, nkv, d, dv, values_in_keys, q.device)
         tile_req, tile_tok0, n_tiles = ctx.q_tiles(tt)
         part_o = part_ml = None
         if splits > 1:
@@ -1827,7 +1833,7 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
             _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kc), _ptr(vc), _ptr(bt), bt.stride(0),
             _ptr(group.table_rows), int(group.page_size), _ptr(ctx.q_start), _ptr(ctx.q_len), _ptr(ctx.kv_len),
             _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), tt, rows, nq, nkv, d, dv, float(scale), _ptr(sinks),
-            _ptr(slopes), 1 if values_in_keys else 0, splits, _ptr(part_o), _ptr(part_ml), _stream())
+            _ptr(slopes), 1 if values_in_keys else 0, splits, _ptr(part_o), _ptr(part_ml), stages, _stream())
         _finish(lib, rc, "attention")
         if splits > 1:
             launch_count += 1        # the merge of the runs

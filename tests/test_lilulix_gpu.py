@@ -453,7 +453,8 @@ def test_configurations_take_both_attention_kernels():
                                                 (8, 1, 576, 512, True), (1, 1, 16, 32, False), (2, 1, 144, 96, True),
                                                 (8, 8, 128, 256, False)])
 @pytest.mark.parametrize("portions,page,mode", [((333,), 16, "rows64"), ((3, 2, 120, 1, 1, 2, 70, 1), 8, "rows16"),
-                                                ((64, 64, 1), 64, "rows64"), ((200, 1, 1, 67, 1), 16, "runs")])
+                                                ((64, 64, 1), 64, "rows64"), ((200, 1, 1, 67, 1), 16, "runs"),
+                                                ((3, 250, 2, 1, 77), 16, "rows32")])
 def test_tensor_core_attention_against_the_plain_softmax(nq, nkv, d, dv, prefix, portions, page, mode):
     """bfloat16 on the tensor-core kernel: random rows through prompts and single tokens, sinks and
     slopes per head, values of their own size or read from the keys' rows, against the plain softmax
@@ -482,7 +483,8 @@ def test_tensor_core_attention_against_the_plain_softmax(nq, nkv, d, dv, prefix,
     G = nq // nkv
     # blocks of 16 rows, blocks of 64 rows, or 16 rows with every tile's keys cut into runs that are merged
     tt16, tt64 = o.rows_attention_tile_tokens(G, 16), o.rows_attention_tile_tokens(G, 64)
-    tt = tt64 if mode == "rows64" and tt64 else tt16
+    tt32 = o.rows_attention_tile_tokens(G, 32)
+    tt = tt64 if mode == "rows64" and tt64 else tt32 if mode == "rows32" and tt32 else tt16
     kc = torch.full((-(-n // page) + 1, nkv, page, d), float("nan"), dtype=torch.bfloat16, device=DEV)
     vc = None if prefix else torch.full((kc.shape[0], nkv, page, dv), float("nan"), dtype=torch.bfloat16, device=DEV)
     pages = list(range(kc.shape[0] - 1, 0, -1))                   # pages handed out from the far end
