@@ -50,7 +50,7 @@ CONFIGS = {
                 vocab=47, width=36, eps=1e-5, buckets=5, mul_prev=2, mul_cur=9, loop=None),
     # a loop of one pass in the middle
     "D": config([biased(heads=2, kv_heads=2, dim=32, scale=0.18, ff=24),
-                 latent(heads=4, dim=16, rot_dim=16, vdim=8, kv_rank=64, base=10000.0, dims=16, scale=0.17, ff=48),
+                 latent(heads=4, dim=16, rot_dim=32, vdim=8, kv_rank=64, base=20000.0, dims=32, scale=0.17, ff=48),
                  biased(heads=8, kv_heads=2, dim=12, scale=0.28, ff=24)],
                 vocab=80, width=48, eps=1e-6, buckets=64, mul_prev=13, mul_cur=1, loop=(1, 2, 1)),
     # many heads over one key/value head (several blocks of heads per token in the tensor-core kernel),
